@@ -12,8 +12,14 @@ What is kept per slot is declared by the model's mixers, one *need* per schedule
              Storage is handed out in pages of PAGE_TOKENS positions, so a sequence holds
              ceil(length / PAGE_TOKENS) pages and nothing more: the cache is sized by the
              number of live tokens, not by slots x longest sequence.
+             `every` > 1: one row per `every` positions instead of one per position (the means of whole blocks of
+             positions: a sequence of n positions holds n // every rows, and pages by rows). `pool` > 0 on a windowed
+             need: positions also stay until their block of `pool` positions is complete, so that whoever forms that
+             block's row can still read them.
   StateNeed  a tensor of fixed shape per sequence (a recurrent state, a running statistic),
              zeroed when the slot is taken.
+  BundleNeed several of these under names, for a schedule entry that keeps more than one thing (keys and values, the
+             rows of whole blocks beside them, and the last inputs of a short convolution).
 
 Entries with the same need share a *group*; each group has storage of its own (its own
 pages, page table and page allocator). A group with a window gives pages back as soon as
@@ -47,26 +53,77 @@ class KvNeed:
     planes: int = 2  # rows kept per position and head: keys and values, or 1 for a mixer whose keys are its values
                      # (the shared latent of a latent attention)
     chunk: int = 0   # > 0: a query sees only the positions of its own block of `chunk` positions
+    every: int = 1   # > 1: one row per `every` positions (row b stands for positions b * every .. b * every + every - 1)
+    pool: int = 0    # > 0: a position also stays until its block of `pool` positions is complete
 
     def first_visible(self, position: int) -> int:
         """Lowest position that a query at `position` sees."""
         first = max(0, position - self.window + 1) if self.window > 0 else 0
         return max(first, position // self.chunk * self.chunk) if self.chunk > 0 else first
 
+    def first_kept(self, length: int) -> int:
+        """Lowest position that is still needed when the sequence holds `length` positions: by the next query's mask, or
+        by the block of `pool` positions that is not complete yet."""
+        first = self.first_visible(length)
+        return min(first, length // self.pool * self.pool) if self.pool > 0 else first
+
+    def rows(self, length: int) -> int:
+        """Rows that a sequence of `length` positions holds."""
+        return length // self.every
+
     def merged(self, other: "KvNeed") -> "KvNeed":
         """What serves this need and a reader with a mask of its own over the same rows: where the masks differ, every
         position is kept."""
         if (other.kv_heads, other.head_dim, other.planes) != (self.kv_heads, self.head_dim, self.planes):
             raise ValueError(f"a layer that reads another layer's cache needs rows of the same shape: {other} against {self}")
-        if (other.window, other.chunk) == (self.window, self.chunk):
+        if (other.window, other.chunk, other.every, other.pool) == (self.window, self.chunk, self.every, self.pool):
             return self
-        return KvNeed(self.kv_heads, self.head_dim, 0, self.planes, 0)
+        if other.every != self.every:
+            raise ValueError(f"a layer that reads another layer's cache needs rows for the same positions: {other} against {self}")
+        return KvNeed(self.kv_heads, self.head_dim, 0, self.planes, 0, self.every)
 
 
 @dataclass(frozen=True)
 class StateNeed:
     shape: tuple
     dtype: torch.dtype = torch.float32
+
+
+@dataclass(frozen=True)
+class BundleNeed:
+    """Several needs of one schedule entry: ((name, need), ...); a need may itself be a bundle. The entry's site is then a
+    `BundleSite` with one site per name."""
+    items: tuple
+
+    def flat(self, prefix: tuple = ()):
+        """(path of names, need) for every KvNeed and StateNeed in the bundle."""
+        for name, need in self.items:
+            if isinstance(need, BundleNeed):
+                yield from need.flat(prefix + (name,))
+            elif need is not None:
+                yield prefix + (name,), need
+
+
+class BundleSite:
+    """The sites of a schedule entry that keeps several things, by the names its `BundleNeed` gave them."""
+
+    def __init__(self):
+        self._sites: dict = {}
+
+    def __getitem__(self, name: str):
+        try:
+            return self._sites[name]
+        except KeyError:
+            raise KeyError(f"this schedule entry keeps nothing called {name!r}; it keeps {', '.join(sorted(self._sites)) or 'nothing'}") from None
+
+    def get(self, name: str, default=None):
+        return self._sites.get(name, default)
+
+    def put(self, path: tuple, site) -> None:
+        if len(path) == 1:
+            self._sites[path[0]] = site
+        else:
+            self._sites.setdefault(path[0], BundleSite()).put(path[1:], site)
 
 
 class KvSite:
@@ -104,8 +161,8 @@ class KvGroup:
         return [lp for lp in range(first_pos // PAGE_TOKENS, (end_pos - 1) // PAGE_TOKENS + 1) if lp not in held]
 
     def first_needed(self, length: int) -> int:
-        """Lowest position that a query at position >= length can still see."""
-        return self.need.first_visible(length)
+        """Lowest ROW that is still needed when the sequence holds `length` positions."""
+        return self.need.first_kept(length) // self.need.every
 
     def grant(self, slot: int, logical_pages: Sequence[int]) -> None:
         ids = self.pages.take(len(logical_pages))
@@ -121,7 +178,7 @@ class KvGroup:
 
     def trim(self, slot: int, length: int) -> None:
         """Give back pages all of whose positions have left the window of every later query."""
-        if self.need.window <= 0 and self.need.chunk <= 0:
+        if (self.need.window <= 0 and self.need.chunk <= 0) or self.need.every > 1:
             return
         keep_from = self.first_needed(length) // PAGE_TOKENS
         gone = [lp for lp in self._held[slot] if lp < keep_from]
@@ -203,24 +260,37 @@ class SequenceCache:
         self.slots = SlotAllocator(self.max_seqs)
         self.lengths = [0] * self.max_seqs
 
-        by_need: dict[object, list[int]] = {}
+        # who keeps what: (schedule entry, path of names inside its bundle; () for an entry with one need) per need
+        by_need: dict[object, list[tuple]] = {}
         for entry, need in enumerate(needs):
-            if need is not None:
-                by_need.setdefault(need, []).append(entry)
+            if isinstance(need, BundleNeed):
+                for path, inner in need.flat():
+                    by_need.setdefault(inner, []).append((entry, path))
+            elif need is not None:
+                by_need.setdefault(need, []).append((entry, ()))
         self.kv_groups: list[KvGroup] = []
         self.state_groups: list[StateGroup] = []
         self._sites: dict[int, object] = {}
-        for need, entries in by_need.items():
+
+        def place(entry: int, path: tuple, site) -> None:
+            if path:
+                self._sites.setdefault(entry, BundleSite()).put(path, site)
+            else:
+                self._sites[entry] = site
+
+        for need, keepers in by_need.items():
             if isinstance(need, KvNeed):
-                group = KvGroup(need, entries, n_pages, self.max_seqs, pages_per_seq, dtype, self.device)
+                # a group of one row per `every` positions is sized by rows: fewer pages, each sequence's last one partly empty
+                pages = n_pages if need.every <= 1 else min(n_pages, n_pages // need.every + self.max_seqs)
+                group = KvGroup(need, keepers, pages, self.max_seqs, pages_per_seq, dtype, self.device)
                 self.kv_groups.append(group)
-                for i, entry in enumerate(entries):
-                    self._sites[entry] = KvSite(group, i)
+                for i, (entry, path) in enumerate(keepers):
+                    place(entry, path, KvSite(group, i))
             elif isinstance(need, StateNeed):
-                group = StateGroup(need, entries, self.max_seqs, self.device)
+                group = StateGroup(need, keepers, self.max_seqs, self.device)
                 self.state_groups.append(group)
-                for i, entry in enumerate(entries):
-                    self._sites[entry] = StateSite(group, i)
+                for i, (entry, path) in enumerate(keepers):
+                    place(entry, path, StateSite(group, i))
             else:
                 raise TypeError(f"unknown cache need {need!r}")
 
@@ -256,8 +326,9 @@ class SequenceCache:
                 self._check_held(slot)
                 if total > self.max_len:
                     raise CacheFull(f"a sequence of {total} tokens exceeds the cache's longest sequence ({self.max_len})")
-                first = min(group.first_needed(self.lengths[slot]), self.lengths[slot])
-                missing = group.pages_missing(slot, first, total)
+                held = group.need.rows(self.lengths[slot])
+                first = min(group.first_needed(self.lengths[slot]), held)
+                missing = group.pages_missing(slot, first, group.need.rows(total))
                 wanted += len(missing)
                 plan.append((slot, missing))
             if wanted > group.pages.n_free:
@@ -291,7 +362,7 @@ class SequenceCache:
     def tokens_free(self) -> int:
         if not self.kv_groups:
             return self.n_pages * PAGE_TOKENS
-        return min(g.pages.n_free for g in self.kv_groups) * PAGE_TOKENS
+        return min(g.pages.n_free * g.need.every for g in self.kv_groups) * PAGE_TOKENS
 
     def live_slots(self) -> list[int]:
         return [s for s in range(self.max_seqs) if self.slots.is_held(s)]
@@ -301,7 +372,10 @@ class SequenceCache:
         total = 0
         for g in self.kv_groups:
             per_token = len(g.entries) * g.need.planes * g.need.kv_heads * g.need.head_dim * g.storage.element_size()
-            total += per_token * sum(n - g.need.first_visible(n - 1) for n in lengths if n > 0)
+            if g.need.every > 1:
+                total += per_token * sum(g.need.rows(n) for n in lengths)
+            else:
+                total += per_token * sum(n - g.need.first_visible(n - 1) for n in lengths if n > 0)
         return total
 
     def storage_bytes(self) -> int:

@@ -5,10 +5,11 @@ from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 from .qwen2 import Qwen2Config
 from .mefepel import MefepelConfig
 from .zebovik import ZebovikConfig
+from .rarevik import RarevikConfig
 from .presets import preset_config, preset_dict, preset_names
 
 __all__ = [
     "resolve_dtype", "ModelConfig", "config_class_for", "config_from_dict", "load_config", "register_architecture",
-    "registered_architectures", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "Qwen2Config", "MefepelConfig", "ZebovikConfig",
+    "registered_architectures", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "Qwen2Config", "MefepelConfig", "ZebovikConfig", "RarevikConfig",
     "preset_config", "preset_dict", "preset_names",
 ]

@@ -53,9 +53,12 @@ class ScheduleEntry:
                 (its weights are then shared, each entry has a cache of its own)
     cache_from  index of an earlier schedule entry whose cache this run reads instead
                 of writing one of its own; None means its own cache
+    enter       index into `ModelSpec.stream_parts`: a part that the whole stream passes through right before this
+                run (it also sees the embedding's output); None means the stream goes in as it is
     """
     layer: int
     cache_from: Optional[int] = None
+    enter: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -76,6 +79,8 @@ class ModelSpec:
     # tensor names that files may hold and that the model does not read (say, the norms of a feed-forward that a layer
     # of this model does not have)
     ignored_tensors: tuple = ()
+    # parts of role "stream" that schedule entries name in `enter`
+    stream_parts: tuple = ()
 
     def validate(self) -> None:
         if not self.schedule:
@@ -84,6 +89,9 @@ class ModelSpec:
             if not 0 <= entry.layer < len(self.layers):
                 raise ValueError(f"model spec: schedule entry {pos} names layer {entry.layer}, "
                                  f"but there are {len(self.layers)} layers")
+            if entry.enter is not None and not 0 <= entry.enter < len(self.stream_parts):
+                raise ValueError(f"model spec: schedule entry {pos} enters through stream part {entry.enter}, "
+                                 f"but there are {len(self.stream_parts)}")
             if entry.cache_from is not None:
                 if not 0 <= entry.cache_from < pos:
                     raise ValueError(f"model spec: schedule entry {pos} reads the cache of entry "

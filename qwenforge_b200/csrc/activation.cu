@@ -133,7 +133,7 @@ QF_EXPORT int qf_scaled_swiglu(int is_bf16, const void* gu, const float* row_sca
 }
 
 // out = act(x + bias): the first half of a feed-forward without a gate. kind 0: the square of relu, 1: tanh-GELU,
-// 2: silu, 3: relu. Float32 inside; bias may be null.
+// 2: silu, 3: relu, 4: GELU in its exact form, z Phi(z) through erf. Float32 inside; bias may be null.
 __device__ __forceinline__ float activate(float z, int kind) {
     if (kind == 0) {
         const float r = fmaxf(z, 0.f);
@@ -141,6 +141,7 @@ __device__ __forceinline__ float activate(float z, int kind) {
     }
     if (kind == 1) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
     if (kind == 2) return z / (1.f + expf(-z));
+    if (kind == 4) return 0.5f * z * (1.f + erff(z * 0.7071067811865476f));
     return fmaxf(z, 0.f);
 }
 
@@ -179,7 +180,7 @@ QF_EXPORT int qf_bias_act(int is_bf16, const void* x, const void* bias, void* ou
                           cudaStream_t stream) {
     const size_t total = (size_t)rows * width;
     if (total == 0) return 0;
-    if (kind < 0 || kind > 3) return (int)cudaErrorInvalidValue;
+    if (kind < 0 || kind > 4) return (int)cudaErrorInvalidValue;
     const size_t most = (size_t)(qf_sm_count() > 0 ? qf_sm_count() : 1) * 16;
     const int blocks = (int)((total + 255) / 256 < most ? (total + 255) / 256 : most);
     if (is_bf16 && width % 8 == 0 && ((uintptr_t)x | (uintptr_t)out | (uintptr_t)bias) % 16 == 0) {
@@ -207,4 +208,30 @@ QF_EXPORT int qf_softcap(float* x, long long total, float cap, cudaStream_t stre
     const size_t most = (size_t)(qf_sm_count() > 0 ? qf_sm_count() : 1) * 16;
     const size_t want = ((size_t)total + 255) / 256;
     return (int)launch_pdl(softcap_kernel, dim3((unsigned)(want < most ? want : most)), dim3(256), 0, stream, x, (size_t)total, cap);
+}
+
+// A gate per token and head on an attention's output, in place: x[t][h][:] *= sigmoid(gate[t][h]). The gates are columns
+// of a wider row (`gate_stride` elements from one token's to the next's); the sigmoid and the product are float32.
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_gate_kernel(T* __restrict__ x, const T* __restrict__ gate, int gate_stride, int n_heads, int head_dim, size_t total) {
+    grid_chain_entry();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t th = i / head_dim, t = th / n_heads, h = th % n_heads;
+        const float g = Num<T>::to_f(gate[t * gate_stride + h]);
+        x[i] = Num<T>::from_f(Num<T>::to_f(x[i]) / (1.f + expf(-g)));
+    }
+}
+
+QF_EXPORT int qf_head_gate(int is_bf16, void* x, const void* gate, int gate_stride, int rows, int n_heads, int head_dim,
+                           cudaStream_t stream) {
+    const size_t total = (size_t)rows * n_heads * head_dim;
+    if (total == 0) return 0;
+    const size_t most = (size_t)(qf_sm_count() > 0 ? qf_sm_count() : 1) * 16;
+    const int blocks = (int)((total + 255) / 256 < most ? (total + 255) / 256 : most);
+    if (is_bf16)
+        return (int)launch_pdl(head_gate_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (bf16*)x, (const bf16*)gate, gate_stride,
+                               n_heads, head_dim, total);
+    return (int)launch_pdl(head_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)x, (const float*)gate, gate_stride,
+                           n_heads, head_dim, total);
 }

@@ -19,6 +19,11 @@
 // themselves (a cache of one plane per page, as a latent attention keeps it: every query head reads the one latent
 // "head" as key and as value).
 //
+// A third: rows of whole blocks (`pool` > 0, with a window). Beside the window's keys a query at p sees one key and value
+// for every block of `pool` positions that lies wholly before its window, blocks b with b * pool + pool - 1 <= p - window;
+// they come from a second cache that holds one row per block (`blocks`), are walked first, in tiles of 32 rows from row
+// 0, and share the softmax with the window's keys.
+//
 // Steps of one token per sequence (decoding) give only sequences x kv heads blocks, each walking a whole sequence. For
 // them the keys are cut into chunks of GEN_CHUNK positions at absolute multiples of GEN_CHUNK: a block per (sequence,
 // kv head, chunk) leaves its rows' maximum, sum and unnormalised output in scratch, and a second kernel folds a row's
@@ -43,13 +48,19 @@ __device__ __forceinline__ int first_visible(int pos, int window, int chunk) {
     return lo;
 }
 
+// Blocks of `pool` positions that lie wholly before the window of a query at `pos`.
+__device__ __forceinline__ int blocks_visible(int pos, int window, int pool) {
+    const int past = pos - window + 1;   // positions before the window
+    return pool > 0 && window > 0 && past >= pool ? past / pool : 0;
+}
+
 template <typename T, bool SPLIT, int MAX_DPL>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, const int* __restrict__ cu_q,
                          const int* __restrict__ tok_pos, const int* __restrict__ slots, KvSite<T> site, int n_heads,
                          int group_chunk, int tokens_per_tile, float scale, int window, float* __restrict__ part_o,
                          float* __restrict__ part_ml, int* err, const float* __restrict__ sinks, int shared_values, int mask_block,
-                         float softcap) {
+                         float softcap, KvSite<T> blocks, int pool) {
     extern __shared__ float smem[];
     const int D = site.head_dim, G = n_heads / site.kv_heads;
     const int chunks = (G + group_chunk - 1) / group_chunk;
@@ -92,7 +103,7 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, const int
     const int lo_min = first_visible(first_pos, window, mask_block);   // rises with the position: the tile's lowest
 
     float m[ROWS_PER_WARP], l[ROWS_PER_WARP], acc[ROWS_PER_WARP][MAX_DPL];
-    int row_pos[ROWS_PER_WARP], row_lo[ROWS_PER_WARP];
+    int row_pos[ROWS_PER_WARP], row_lo[ROWS_PER_WARP], row_blocks[ROWS_PER_WARP];
 #pragma unroll
     for (int i = 0; i < ROWS_PER_WARP; ++i) {
         m[i] = -FLT_MAX;
@@ -102,6 +113,7 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, const int
         const int r = warp + i * WARPS;
         row_pos[i] = r < n_rows ? first_pos + r / n_g : -1;
         row_lo[i] = row_pos[i] >= 0 ? first_visible(row_pos[i], window, mask_block) : 0;
+        row_blocks[i] = row_pos[i] >= 0 ? blocks_visible(row_pos[i], window, pool) : 0;
     }
     const int dpl = (D + 31) / 32;
 
@@ -112,17 +124,23 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, const int
         k_begin = max(k_begin, c0);
         k_last = min(k_last, c0 + GEN_CHUNK - 1);
     }
-    for (int k0 = k_begin; k0 <= k_last; k0 += KT) {
+    // two walks with the same body: the rows of whole blocks first (phase 0, when there are any), then the positions
+    const int blocks_most = SPLIT ? 0 : blocks_visible(last_pos, window, pool);
+    for (int phase = blocks_most > 0 ? 0 : 1; phase < 2; ++phase) {
+    const KvSite<T>& from = phase == 0 ? blocks : site;
+    const int walk_begin = phase == 0 ? 0 : k_begin, walk_last = phase == 0 ? blocks_most - 1 : k_last;
+    const int stage_lo = phase == 0 ? 0 : lo_min, stage_hi = phase == 0 ? blocks_most - 1 : last_pos;
+    for (int k0 = walk_begin; k0 <= walk_last; k0 += KT) {
         __syncthreads();  // the previous tile is consumed (and q_s is complete on the first pass)
         // stage keys k0 .. k0+KT-1 that some row may read; zero the rest so that 0 * garbage cannot arise
         for (int i = threadIdx.x; i < KT * D; i += blockDim.x) {
             const int j = i / D, d = i % D, kj = k0 + j;
             float kval = 0.f, vval = 0.f;
-            if (kj >= lo_min && kj <= last_pos) {
-                const T* kp = kv_row(site, slot, kj, kvh, 0);
+            if (kj >= stage_lo && kj <= stage_hi) {
+                const T* kp = kv_row(from, slot, kj, kvh, 0);
                 if (kp) {
                     kval = Num<T>::to_f(kp[d]);
-                    vval = shared_values ? kval : Num<T>::to_f(kp[(size_t)site.kv_heads * QF_PAGE * D + d]);
+                    vval = shared_values ? kval : Num<T>::to_f(kp[(size_t)from.kv_heads * QF_PAGE * D + d]);
                 } else if (d == 0) {
                     atomicOr(err, QF_ERR_NO_PAGE);
                 }
@@ -136,14 +154,15 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, const int
         for (int i = 0; i < ROWS_PER_WARP; ++i) {
             const int r = warp + i * WARPS;
             if (r >= n_rows) continue;
-            if (k0 > row_pos[i] || k0 + KT <= row_lo[i]) continue;  // no visible key of this tile (warp-uniform)
+            const int hi = phase == 0 ? row_blocks[i] - 1 : row_pos[i], lo = phase == 0 ? 0 : row_lo[i];
+            if (k0 > hi || k0 + KT <= lo) continue;  // no visible key of this tile (warp-uniform)
             const float* qr = q_s + r * D;
             const float* kr = k_s + lane * ldk;
             float s = 0.f;
             for (int d = 0; d < D; ++d) s = fmaf(qr[d], kr[d], s);
             s *= scale;
             if (softcap > 0.f) s = softcap * tanhf(s / softcap);
-            const bool visible = kj <= row_pos[i] && kj >= row_lo[i];
+            const bool visible = kj <= hi && kj >= lo;
             s = visible ? s : -FLT_MAX;
             const float m_new = fmaxf(m[i], warp_max(s));
             const float p = visible ? expf(s - m_new) : 0.f;
@@ -161,6 +180,7 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, const int
                 }
             }
         }
+    }
     }
 #pragma unroll
     for (int i = 0; i < ROWS_PER_WARP; ++i) {
@@ -233,8 +253,10 @@ template <typename T, int MAX_DPL>
 static int launch(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots, void* base,
                   const int* table, long long page_elems, int table_stride, int kv_heads, int head_dim, int n_heads,
                   int n_seqs, int max_q_len, float scale, int window, int* err, const float* sinks, int shared_values,
-                  int chunk, float softcap, cudaStream_t stream) {
+                  int chunk, float softcap, void* blocks_base, const int* blocks_table, long long blocks_page_elems,
+                  int blocks_table_stride, int pool, cudaStream_t stream) {
     if (n_seqs <= 0 || max_q_len <= 0) return 0;
+    if (pool > 0 && (!blocks_base || !blocks_table || window <= 0 || shared_values)) return (int)cudaErrorInvalidValue;
     if (head_dim > 32 * MAX_DPL || kv_heads <= 0 || n_heads % kv_heads) return (int)cudaErrorInvalidValue;
     const int G = n_heads / kv_heads;
     const int group_chunk = G < MAX_ROWS ? G : MAX_ROWS;
@@ -249,7 +271,8 @@ static int launch(const void* q, void* out, const int* cu_q, const int* tok_pos,
     dim3 grid((max_q_len + tokens_per_tile - 1) / tokens_per_tile, kv_heads * chunks, n_seqs);
     attention_generic_kernel<T, false, MAX_DPL><<<grid, WARPS * 32, smem, stream>>>(
         (const T*)q, (T*)out, cu_q, tok_pos, slots, site, n_heads, group_chunk, tokens_per_tile, scale, window, nullptr, nullptr,
-        err, sinks, shared_values, chunk, softcap);
+        err, sinks, shared_values, chunk, softcap,
+        KvSite<T>{(T*)blocks_base, blocks_table, blocks_page_elems, blocks_table_stride, kv_heads, head_dim}, pool);
     return (int)cudaGetLastError();
 }
 
@@ -271,7 +294,7 @@ static int launch_decode(const void* q, void* out, const int* cu_q, const int* t
     KvSite<T> site{(T*)base, table, page_elems, table_stride, kv_heads, head_dim};
     attention_generic_kernel<T, true, MAX_DPL><<<dim3(n_chunks, kv_heads * chunks, n_seqs), WARPS * 32, smem, stream>>>(
         (const T*)q, (T*)out, cu_q, tok_pos, slots, site, n_heads, group_chunk, 1, scale, window, part_o, part_ml, err, nullptr,
-        shared_values, chunk, softcap);
+        shared_values, chunk, softcap, KvSite<T>{nullptr, nullptr, 0, 0, kv_heads, head_dim}, 0);
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     attention_generic_fold_kernel<T><<<dim3(n_heads, n_seqs), 64, 0, stream>>>((T*)out, cu_q, tok_pos, slots, n_heads, head_dim,
@@ -288,13 +311,28 @@ static int launch_decode(const void* q, void* out, const int* cu_q, const int* t
     return is_bf16 ? FN<bf16, MAX_DPL_WIDE>(__VA_ARGS__) : FN<float, MAX_DPL_WIDE>(__VA_ARGS__);
 
 // chunk: > 0 limits a query to the keys of its own block of that many positions; softcap: > 0 caps the scores.
+// pool > 0: rows of whole blocks of `pool` positions, kept in a second cache of the same head shape (blocks_*), join the
+// window's keys (see the top of the file).
+QF_EXPORT int qf_attention_generic_pooled(int is_bf16, const void* q, void* out, const int* cu_q, const int* tok_pos,
+                                          const int* slots, void* base, const int* table, long long page_elems,
+                                          int table_stride, int kv_heads, int head_dim, int n_heads, int n_seqs,
+                                          int max_q_len, float scale, int window, int* err, const float* sinks,
+                                          int shared_values, int chunk, float softcap, void* blocks_base,
+                                          const int* blocks_table, long long blocks_page_elems, int blocks_table_stride, int pool,
+                                          cudaStream_t stream) {
+    QF_GENERIC_DISPATCH(launch, q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads, head_dim,
+                        n_heads, n_seqs, max_q_len, scale, window, err, sinks, shared_values, chunk, softcap, blocks_base,
+                        blocks_table, blocks_page_elems, blocks_table_stride, pool, stream)
+}
+
 QF_EXPORT int qf_attention_generic_masked(int is_bf16, const void* q, void* out, const int* cu_q, const int* tok_pos,
                                           const int* slots, void* base, const int* table, long long page_elems,
                                           int table_stride, int kv_heads, int head_dim, int n_heads, int n_seqs,
                                           int max_q_len, float scale, int window, int* err, const float* sinks,
                                           int shared_values, int chunk, float softcap, cudaStream_t stream) {
-    QF_GENERIC_DISPATCH(launch, q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads, head_dim,
-                        n_heads, n_seqs, max_q_len, scale, window, err, sinks, shared_values, chunk, softcap, stream)
+    return qf_attention_generic_pooled(is_bf16, q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads,
+                                       head_dim, n_heads, n_seqs, max_q_len, scale, window, err, sinks, shared_values, chunk,
+                                       softcap, nullptr, nullptr, 0, 0, 0, stream);
 }
 
 QF_EXPORT int qf_attention_generic_ex(int is_bf16, const void* q, void* out, const int* cu_q, const int* tok_pos,

@@ -23,13 +23,15 @@
 
 // One token's choice: the `top` experts with the largest scores (the larger logit is the larger score; ties go to the
 // lower index) and their weights.
-__device__ __forceinline__ void moe_choose(const float* z, int n_experts, int top, int softmax_scores, int renormalize,
-                                           int* chosen, float* weight) {
+// `bias` (float32 per expert, or null) is added to the logits before anything else looks at them.
+__device__ __forceinline__ void moe_choose(const float* z_raw, const float* bias, int n_experts, int top, int softmax_scores,
+                                           int renormalize, int* chosen, float* weight) {
+    auto z = [&](int e) { return bias ? z_raw[e] + bias[e] : z_raw[e]; };
     float top_z = -FLT_MAX, denom = 1.f;
     if (softmax_scores) {
-        for (int e = 0; e < n_experts; ++e) top_z = fmaxf(top_z, z[e]);
+        for (int e = 0; e < n_experts; ++e) top_z = fmaxf(top_z, z(e));
         denom = 0.f;
-        for (int e = 0; e < n_experts; ++e) denom += expf(z[e] - top_z);
+        for (int e = 0; e < n_experts; ++e) denom += expf(z(e) - top_z);
     }
     float total = 0.f;
     for (int k = 0; k < top; ++k) {
@@ -38,9 +40,9 @@ __device__ __forceinline__ void moe_choose(const float* z, int n_experts, int to
         for (int e = 0; e < n_experts; ++e) {
             bool taken = false;
             for (int j = 0; j < k; ++j) taken |= chosen[j] == e;
-            if (!taken && (best < 0 || z[e] > best_z)) {
+            if (!taken && (best < 0 || z(e) > best_z)) {
                 best = e;
-                best_z = z[e];
+                best_z = z(e);
             }
         }
         chosen[k] = best;
@@ -59,7 +61,8 @@ moe_plan_kernel(const float* logits, int n_tokens, int n_experts, int top, int s
                 int* __restrict__ pair_expert, float* __restrict__ pair_weight, int* __restrict__ sorted_token,
                 float* __restrict__ sorted_weight, int* __restrict__ dest, int* __restrict__ offsets,
                 int* __restrict__ tile_group, int* __restrict__ tile_row0, int* __restrict__ n_tiles, int max_tiles,
-                int tile_rows, const void* __restrict__ x, const void* __restrict__ router, int width, int x_is_bf16) {
+                int tile_rows, const void* __restrict__ x, const void* __restrict__ router, int width, int x_is_bf16,
+                const float* __restrict__ bias) {
     grid_chain_entry();
     extern __shared__ int shared[];
     int* counts = shared;                   // [experts]: rows per expert, then every expert's first row
@@ -108,7 +111,7 @@ moe_plan_kernel(const float* logits, int n_tokens, int n_experts, int top, int s
     for (int t = threadIdx.x; t < n_tokens; t += blockDim.x) {
         int chosen[MOE_MAX_TOP];
         float weight[MOE_MAX_TOP];
-        moe_choose(logits + (size_t)t * n_experts, n_experts, top, softmax_scores, renormalize, chosen, weight);
+        moe_choose(logits + (size_t)t * n_experts, bias, n_experts, top, softmax_scores, renormalize, chosen, weight);
         for (int k = 0; k < top; ++k) {
             const int pair = t * top + k;
             pair_expert[pair] = chosen[k];
@@ -157,7 +160,7 @@ moe_plan_kernel(const float* logits, int n_tokens, int n_experts, int top, int s
 __global__ void __launch_bounds__(256)
 moe_route_kernel(const float* __restrict__ logits, int n_tokens, int n_experts, int top, int softmax_scores, int renormalize,
                  int* __restrict__ pair_expert, float* __restrict__ pair_weight, int* __restrict__ dest,
-                 int* __restrict__ expert_rows) {
+                 int* __restrict__ expert_rows, const float* __restrict__ bias) {
     grid_chain_entry();
     extern __shared__ int shared[];
     int* counts = shared;               // [experts] pairs of this block
@@ -168,7 +171,7 @@ moe_route_kernel(const float* __restrict__ logits, int n_tokens, int n_experts, 
     int chosen[MOE_MAX_TOP], rank[MOE_MAX_TOP];
     float weight[MOE_MAX_TOP];
     if (t < n_tokens) {
-        moe_choose(logits + (size_t)t * n_experts, n_experts, top, softmax_scores, renormalize, chosen, weight);
+        moe_choose(logits + (size_t)t * n_experts, bias, n_experts, top, softmax_scores, renormalize, chosen, weight);
         for (int k = 0; k < top; ++k) rank[k] = atomicAdd(&counts[chosen[k]], 1);
     }
     __syncthreads();
@@ -246,10 +249,13 @@ moe_gather_kernel(const T* __restrict__ x, const int* __restrict__ sorted_token,
 template <typename T>
 __global__ void __launch_bounds__(128)
 moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ dest, const float* __restrict__ sorted_weight,
-                   T* __restrict__ out, int n_tokens, int top, int width, int scale_output) {
+                   T* __restrict__ out, int n_tokens, int top, int width, int scale_output, const T* __restrict__ extra,
+                   const float* __restrict__ extra_gate) {
     grid_chain_entry();
     const int t = blockIdx.x;
     if (t >= n_tokens) return;
+    // an output that every token gets beside its chosen ones (`extra`), under a sigmoid gate of one logit per token
+    const float share = extra ? (extra_gate ? 1.f / (1.f + expf(-extra_gate[t])) : 1.f) : 0.f;
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
         float sum = 0.f;
         for (int k = 0; k < top; ++k) {
@@ -257,6 +263,7 @@ moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ dest, const 
             const float v = Num<T>::to_f(y[(size_t)row * width + c]);
             sum += scale_output ? v * sorted_weight[row] : v;
         }
+        if (extra) sum = fmaf(share, Num<T>::to_f(extra[(size_t)t * width + c]), sum);
         out[(size_t)t * width + c] = Num<T>::from_f(sum);
     }
 }
@@ -265,17 +272,28 @@ moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ dest, const 
 // tile_group and tile_row0 max_tiles >= ceil(pairs / tile_rows) + n_experts. Either `logits` float32 [n_tokens][n_experts]
 // is given, or x [n_tokens][width] and router [n_experts][width] (both bfloat16 or both float32), from which the kernel makes
 // the logits itself in shared memory (n_tokens * n_experts <= 8192).
-QF_EXPORT int qf_moe_plan(const float* logits, int n_tokens, int n_experts, int top, int softmax_scores, int renormalize,
-                          int* pair_expert, float* pair_weight, int* sorted_token, float* sorted_weight, int* dest,
-                          int* offsets, int* tile_group, int* tile_row0, int* n_tiles, int max_tiles, int tile_rows,
-                          const void* x, const void* router, int width, int x_is_bf16, cudaStream_t stream) {
+// bias: float32 [n_experts] added to the logits, or null.
+QF_EXPORT int qf_moe_plan_biased(const float* logits, int n_tokens, int n_experts, int top, int softmax_scores, int renormalize,
+                                 int* pair_expert, float* pair_weight, int* sorted_token, float* sorted_weight, int* dest,
+                                 int* offsets, int* tile_group, int* tile_row0, int* n_tiles, int max_tiles, int tile_rows,
+                                 const void* x, const void* router, int width, int x_is_bf16, const float* bias,
+                                 cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (top < 1 || top > MOE_MAX_TOP || top > n_experts || n_experts > 8192 || tile_rows <= 0) return (int)cudaErrorInvalidValue;
     if (!logits && !(x && router && (long long)n_tokens * n_experts <= 8192)) return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)(2 * n_experts + 1) * sizeof(int) + (logits ? 0 : (size_t)n_tokens * n_experts * sizeof(float));
     return (int)launch_pdl(moe_plan_kernel, dim3(1), dim3(MOE_PLAN_THREADS), smem, stream, logits, n_tokens, n_experts, top,
                            softmax_scores, renormalize, pair_expert, pair_weight, sorted_token, sorted_weight, dest, offsets,
-                           tile_group, tile_row0, n_tiles, max_tiles, tile_rows, logits ? nullptr : x, router, width, x_is_bf16);
+                           tile_group, tile_row0, n_tiles, max_tiles, tile_rows, logits ? nullptr : x, router, width, x_is_bf16, bias);
+}
+
+QF_EXPORT int qf_moe_plan(const float* logits, int n_tokens, int n_experts, int top, int softmax_scores, int renormalize,
+                          int* pair_expert, float* pair_weight, int* sorted_token, float* sorted_weight, int* dest,
+                          int* offsets, int* tile_group, int* tile_row0, int* n_tiles, int max_tiles, int tile_rows,
+                          const void* x, const void* router, int width, int x_is_bf16, cudaStream_t stream) {
+    return qf_moe_plan_biased(logits, n_tokens, n_experts, top, softmax_scores, renormalize, pair_expert, pair_weight, sorted_token,
+                              sorted_weight, dest, offsets, tile_group, tile_row0, n_tiles, max_tiles, tile_rows, x, router, width,
+                              x_is_bf16, nullptr, stream);
 }
 
 QF_EXPORT int qf_moe_gather(int is_bf16, const void* x, const int* sorted_token, const float* sorted_weight, void* out,
@@ -288,27 +306,35 @@ QF_EXPORT int qf_moe_gather(int is_bf16, const void* x, const int* sorted_token,
                            sorted_weight, (float*)out, n_rows, width, scale_input);
 }
 
-QF_EXPORT int qf_moe_combine(int is_bf16, const void* y, const int* dest, const float* sorted_weight, void* out, int n_tokens,
-                             int top, int width, int scale_output, cudaStream_t stream) {
+// extra: [n_tokens][width] added to every token's sum (or null), times sigmoid(extra_gate[t]) where extra_gate (float32
+// [n_tokens]) is given.
+QF_EXPORT int qf_moe_combine_shared(int is_bf16, const void* y, const int* dest, const float* sorted_weight, void* out, int n_tokens,
+                                    int top, int width, int scale_output, const void* extra, const float* extra_gate,
+                                    cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (is_bf16)
         return (int)launch_pdl(moe_combine_kernel<bf16>, dim3(n_tokens), dim3(128), 0, stream, (const bf16*)y, dest, sorted_weight,
-                               (bf16*)out, n_tokens, top, width, scale_output);
+                               (bf16*)out, n_tokens, top, width, scale_output, (const bf16*)extra, extra_gate);
     return (int)launch_pdl(moe_combine_kernel<float>, dim3(n_tokens), dim3(128), 0, stream, (const float*)y, dest, sorted_weight,
-                           (float*)out, n_tokens, top, width, scale_output);
+                           (float*)out, n_tokens, top, width, scale_output, (const float*)extra, extra_gate);
+}
+
+QF_EXPORT int qf_moe_combine(int is_bf16, const void* y, const int* dest, const float* sorted_weight, void* out, int n_tokens,
+                             int top, int width, int scale_output, cudaStream_t stream) {
+    return qf_moe_combine_shared(is_bf16, y, dest, sorted_weight, out, n_tokens, top, width, scale_output, nullptr, nullptr, stream);
 }
 
 // The plan of a long step by three launches (see moe_route_kernel). expert_rows: int32 [n_experts], zero before the call.
-QF_EXPORT int qf_moe_plan_long(const float* logits, int n_tokens, int n_experts, int top, int softmax_scores, int renormalize,
-                               int* pair_expert, float* pair_weight, int* sorted_token, float* sorted_weight, int* dest,
-                               int* offsets, int* tile_group, int* tile_row0, int* n_tiles, int max_tiles, int tile_rows,
-                               int* expert_rows, cudaStream_t stream) {
+QF_EXPORT int qf_moe_plan_long_biased(const float* logits, int n_tokens, int n_experts, int top, int softmax_scores,
+                                      int renormalize, int* pair_expert, float* pair_weight, int* sorted_token,
+                                      float* sorted_weight, int* dest, int* offsets, int* tile_group, int* tile_row0, int* n_tiles,
+                                      int max_tiles, int tile_rows, int* expert_rows, const float* bias, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (top < 1 || top > MOE_MAX_TOP || top > n_experts || n_experts > 4096 || tile_rows <= 0 || !logits || !expert_rows)
         return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)(2 * n_experts + 1) * sizeof(int);
     int code = (int)launch_pdl(moe_route_kernel, dim3((n_tokens + 255) / 256), dim3(256), smem, stream, logits, n_tokens, n_experts,
-                               top, softmax_scores, renormalize, pair_expert, pair_weight, dest, expert_rows);
+                               top, softmax_scores, renormalize, pair_expert, pair_weight, dest, expert_rows, bias);
     if (code) return code;
     code = (int)launch_pdl(moe_offsets_kernel, dim3(1), dim3(256), smem, stream, (const int*)expert_rows, n_experts, offsets,
                            tile_group, tile_row0, n_tiles, max_tiles, tile_rows);
@@ -316,4 +342,13 @@ QF_EXPORT int qf_moe_plan_long(const float* logits, int n_tokens, int n_experts,
     const int pairs = n_tokens * top;
     return (int)launch_pdl(moe_place_kernel, dim3((pairs + 255) / 256), dim3(256), 0, stream, (const int*)pair_expert,
                            (const float*)pair_weight, (const int*)offsets, dest, sorted_token, sorted_weight, pairs, top);
+}
+
+QF_EXPORT int qf_moe_plan_long(const float* logits, int n_tokens, int n_experts, int top, int softmax_scores, int renormalize,
+                               int* pair_expert, float* pair_weight, int* sorted_token, float* sorted_weight, int* dest,
+                               int* offsets, int* tile_group, int* tile_row0, int* n_tiles, int max_tiles, int tile_rows,
+                               int* expert_rows, cudaStream_t stream) {
+    return qf_moe_plan_long_biased(logits, n_tokens, n_experts, top, softmax_scores, renormalize, pair_expert, pair_weight,
+                                   sorted_token, sorted_weight, dest, offsets, tile_group, tile_row0, n_tiles, max_tiles, tile_rows,
+                                   expert_rows, nullptr, stream);
 }

@@ -297,3 +297,119 @@ QF_EXPORT int qf_sandwich_norm(int is_bf16, float* hidden, const void* y, const 
     return is_bf16 ? sandwich_launch<bf16>(hidden, y, post_weight, eps_post, next_weight, eps_next, out, rows, width, dest, top, row_weight, stream)
                    : sandwich_launch<float>(hidden, y, post_weight, eps_post, next_weight, eps_next, out, rows, width, dest, top, row_weight, stream);
 }
+
+// ------------------------------------------------------------------------------------------------------------------
+// Dynamic Tanh in the place of a norm: no mean and no variance, element by element
+//   hidden += (a + b) (each if given);  out = tanh(alpha * hidden) * weight + bias
+// The sum into the stream and the tanh are float32; `out` has the activation type. Two pending outputs are taken because
+// a layer whose sublayers both read the one norm leaves two.
+template <typename T>
+__global__ void __launch_bounds__(256)
+add_dyt_norm_kernel(float* __restrict__ hidden, const T* __restrict__ a, const T* __restrict__ b, const T* __restrict__ weight,
+                    const T* __restrict__ bias, float alpha, T* __restrict__ out, size_t total, int width) {
+    grid_chain_entry();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        float v = hidden[i];
+        if (a || b) {
+            v += (a ? Num<T>::to_f(a[i]) : 0.f) + (b ? Num<T>::to_f(b[i]) : 0.f);
+            hidden[i] = v;
+        }
+        const int c = (int)(i % width);
+        out[i] = Num<T>::from_f(fmaf(tanhf(alpha * v), Num<T>::to_f(weight[c]), Num<T>::to_f(bias[c])));
+    }
+}
+
+// Four elements per thread: width % 4 == 0 and pointers that 16-byte (float32) / 8-byte (bfloat16) accesses can address.
+template <typename T>
+__global__ void __launch_bounds__(256)
+add_dyt_norm_vec_kernel(float* __restrict__ hidden, const T* __restrict__ a, const T* __restrict__ b, const T* __restrict__ weight,
+                        const T* __restrict__ bias, float alpha, T* __restrict__ out, size_t total4, int width4) {
+    grid_chain_entry();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (size_t)gridDim.x * blockDim.x) {
+        float4 v = *reinterpret_cast<const float4*>(hidden + i * 4);
+        if (a || b) {
+            const float4 x = a ? Vec4<T>::load(a + i * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            const float4 y = b ? Vec4<T>::load(b + i * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            v.x += x.x + y.x;
+            v.y += x.y + y.y;
+            v.z += x.z + y.z;
+            v.w += x.w + y.w;
+            *reinterpret_cast<float4*>(hidden + i * 4) = v;
+        }
+        const int c = (int)(i % width4) * 4;
+        const float4 w = Vec4<T>::load(weight + c), s = Vec4<T>::load(bias + c);
+        Vec4<T>::store(out + i * 4, make_float4(fmaf(tanhf(alpha * v.x), w.x, s.x), fmaf(tanhf(alpha * v.y), w.y, s.y),
+                                                fmaf(tanhf(alpha * v.z), w.z, s.z), fmaf(tanhf(alpha * v.w), w.w, s.w)));
+    }
+}
+
+static inline int elementwise_blocks(size_t items) {
+    const size_t most = (size_t)(qf_sm_count() > 0 ? qf_sm_count() : 1) * 16;
+    const size_t want = (items + 255) / 256;
+    return (int)(want < most ? (want ? want : 1) : most);
+}
+
+template <typename T>
+static int launch_dyt(float* hidden, const void* a, const void* b, const void* weight, const void* bias, float alpha, void* out,
+                      int rows, int width, cudaStream_t stream) {
+    const size_t total = (size_t)rows * width;
+    const uintptr_t all = (uintptr_t)hidden | (uintptr_t)a | (uintptr_t)b | (uintptr_t)weight | (uintptr_t)bias | (uintptr_t)out;
+    if (width % 4 == 0 && all % 16 == 0)
+        return (int)launch_pdl(add_dyt_norm_vec_kernel<T>, dim3(elementwise_blocks(total / 4)), dim3(256), 0, stream, hidden,
+                               (const T*)a, (const T*)b, (const T*)weight, (const T*)bias, alpha, (T*)out, total / 4, width / 4);
+    return (int)launch_pdl(add_dyt_norm_kernel<T>, dim3(elementwise_blocks(total)), dim3(256), 0, stream, hidden, (const T*)a,
+                           (const T*)b, (const T*)weight, (const T*)bias, alpha, (T*)out, total, width);
+}
+
+// hidden: float32 [rows][width], updated in place when a or b is given; a, b, weight, bias, out: activation dtype.
+QF_EXPORT int qf_add_dyt_norm(int is_bf16, float* hidden, const void* a, const void* b, const void* weight, const void* bias,
+                              float alpha, void* out, int rows, int width, cudaStream_t stream) {
+    if (rows <= 0 || width <= 0) return 0;
+    return is_bf16 ? launch_dyt<bf16>(hidden, a, b, weight, bias, alpha, out, rows, width, stream)
+                   : launch_dyt<float>(hidden, a, b, weight, bias, alpha, out, rows, width, stream);
+}
+
+// hidden += (a + b): two pending outputs of one layer, summed with each other first, then into the float32 stream.
+template <typename T>
+__global__ void __launch_bounds__(256)
+residual_add_pair_kernel(float* __restrict__ hidden, const T* __restrict__ a, const T* __restrict__ b, size_t total) {
+    grid_chain_entry();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+        hidden[i] += (a ? Num<T>::to_f(a[i]) : 0.f) + (b ? Num<T>::to_f(b[i]) : 0.f);
+}
+
+QF_EXPORT int qf_residual_add_pair(int is_bf16, float* hidden, const void* a, const void* b, long long n, cudaStream_t stream) {
+    if (n <= 0 || (!a && !b)) return 0;
+    if (is_bf16)
+        return (int)launch_pdl(residual_add_pair_kernel<bf16>, dim3(elementwise_blocks((size_t)n)), dim3(256), 0, stream, hidden,
+                               (const bf16*)a, (const bf16*)b, (size_t)n);
+    return (int)launch_pdl(residual_add_pair_kernel<float>, dim3(elementwise_blocks((size_t)n)), dim3(256), 0, stream, hidden,
+                           (const float*)a, (const float*)b, (size_t)n);
+}
+
+// Rows of two float32 streams side by side in the activation dtype, as a product's input:
+//   out[t] = [ hidden[t] + (a[t] + b[t]) | other[t] ]     (a, b: pending outputs, each if given; hidden is not changed)
+template <typename T>
+__global__ void __launch_bounds__(256)
+stream_pair_kernel(const float* __restrict__ hidden, const T* __restrict__ a, const T* __restrict__ b,
+                   const float* __restrict__ other, T* __restrict__ out, size_t total, int width) {
+    grid_chain_entry();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / width, c = i % width;
+        float v = hidden[i];
+        if (a || b) v += (a ? Num<T>::to_f(a[i]) : 0.f) + (b ? Num<T>::to_f(b[i]) : 0.f);
+        out[t * 2 * width + c] = Num<T>::from_f(v);
+        out[t * 2 * width + width + c] = Num<T>::from_f(other[i]);
+    }
+}
+
+QF_EXPORT int qf_stream_pair(int is_bf16, const float* hidden, const void* a, const void* b, const float* other, void* out,
+                             int rows, int width, cudaStream_t stream) {
+    const size_t total = (size_t)rows * width;
+    if (total == 0) return 0;
+    if (is_bf16)
+        return (int)launch_pdl(stream_pair_kernel<bf16>, dim3(elementwise_blocks(total)), dim3(256), 0, stream, hidden, (const bf16*)a,
+                               (const bf16*)b, other, (bf16*)out, total, width);
+    return (int)launch_pdl(stream_pair_kernel<float>, dim3(elementwise_blocks(total)), dim3(256), 0, stream, hidden, (const float*)a,
+                           (const float*)b, other, (float*)out, total, width);
+}

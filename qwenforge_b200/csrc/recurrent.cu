@@ -414,7 +414,7 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ x, int x_stride, c
                                         const float* __restrict__ bias, const int* __restrict__ cu_q,
                                         const int* __restrict__ tok_seq, const int* __restrict__ slots,
                                         const float* __restrict__ state, long long slot_stride, long long offset, int taps,
-                                        int n_tokens, int channels, T* __restrict__ out) {
+                                        int n_tokens, int channels, T* __restrict__ out, int plain) {
     grid_chain_entry();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (long long)n_tokens * channels) return;
@@ -429,7 +429,7 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ x, int x_stride, c
         else if (before) u = before[(size_t)(taps - 1 + at - back) * channels + c];
         z = fmaf(weight[(size_t)c * taps + j], u, z);
     }
-    out[(size_t)t * channels + c] = Num<T>::from_f(z / (1.f + expf(-z)));
+    out[(size_t)t * channels + c] = Num<T>::from_f(plain ? z : z / (1.f + expf(-z)));
 }
 
 template <typename T>
@@ -454,11 +454,11 @@ __global__ void conv_state_kernel(const T* __restrict__ x, int x_stride, const i
 template <typename T>
 static int launch_conv(const void* x, int x_stride, const float* weight, const float* bias, const int* cu_q, const int* tok_seq,
                        const int* slots, int n_seqs, float* state, long long slot_stride, long long offset, int taps,
-                       int n_tokens, int channels, void* out, cudaStream_t stream) {
+                       int n_tokens, int channels, void* out, int plain, cudaStream_t stream) {
     const long long total = (long long)n_tokens * channels;
     cudaError_t e = launch_pdl(causal_conv_silu_kernel<T>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream,
                                (const T*)x, x_stride, weight, bias, cu_q, tok_seq, slots, (const float*)state, slot_stride, offset,
-                               taps, n_tokens, channels, (T*)out);
+                               taps, n_tokens, channels, (T*)out, plain);
     if (e != cudaSuccess || taps <= 1) return (int)e;
     const long long pairs = (long long)n_seqs * channels;
     // launched the ordinary way: it must not start before every block of the convolution has read the old state
@@ -467,14 +467,23 @@ static int launch_conv(const void* x, int x_stride, const float* weight, const f
     return (int)cudaGetLastError();
 }
 
+// plain: 1 leaves the activation out (the convolution alone).
+QF_EXPORT int qf_causal_conv(int is_bf16, const void* x, int x_stride, const float* weight, const float* bias,
+                             const int* cu_q, const int* tok_seq, const int* slots, int n_seqs, float* state,
+                             long long slot_stride, long long offset, int taps, int n_tokens, int channels, void* out, int plain,
+                             cudaStream_t stream) {
+    if (n_tokens <= 0 || channels <= 0) return 0;
+    if (taps < 1 || taps > CONV_MAX_TAPS) return (int)cudaErrorInvalidValue;
+    return is_bf16 ? launch_conv<bf16>(x, x_stride, weight, bias, cu_q, tok_seq, slots, n_seqs, state, slot_stride, offset, taps,
+                                       n_tokens, channels, out, plain, stream)
+                   : launch_conv<float>(x, x_stride, weight, bias, cu_q, tok_seq, slots, n_seqs, state, slot_stride, offset, taps,
+                                        n_tokens, channels, out, plain, stream);
+}
+
 QF_EXPORT int qf_causal_conv_silu(int is_bf16, const void* x, int x_stride, const float* weight, const float* bias,
                                   const int* cu_q, const int* tok_seq, const int* slots, int n_seqs, float* state,
                                   long long slot_stride, long long offset, int taps, int n_tokens, int channels, void* out,
                                   cudaStream_t stream) {
-    if (n_tokens <= 0 || channels <= 0) return 0;
-    if (taps < 1 || taps > CONV_MAX_TAPS) return (int)cudaErrorInvalidValue;
-    return is_bf16 ? launch_conv<bf16>(x, x_stride, weight, bias, cu_q, tok_seq, slots, n_seqs, state, slot_stride, offset, taps,
-                                       n_tokens, channels, out, stream)
-                   : launch_conv<float>(x, x_stride, weight, bias, cu_q, tok_seq, slots, n_seqs, state, slot_stride, offset, taps,
-                                        n_tokens, channels, out, stream);
+    return qf_causal_conv(is_bf16, x, x_stride, weight, bias, cu_q, tok_seq, slots, n_seqs, state, slot_stride, offset, taps,
+                          n_tokens, channels, out, 0, stream);
 }

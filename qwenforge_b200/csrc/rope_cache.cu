@@ -222,10 +222,13 @@ QF_EXPORT int qf_rope_cache_write(int is_bf16, const void* qkv, const void* bias
                                    stream);
 }
 
-// The same with what other kinds of attention need: after the rotation every q and k head may be divided by its root
-// mean square over its first `norm_dim` components (eps inside the root; eps < 0: no norm), and the rows may hold queries
-// only (`has_kv` 0: a layer that reads another layer's keys and values). One warp per (token, head): the head's
-// components stay in registers between the rotation and the norm. Value heads are copied (with their bias) as they are.
+// The same with what other kinds of attention need. Every q and k head may be divided by its root mean square over its
+// first `norm_dim` components (eps inside the root; eps < 0: no norm): after the rotation and without a weight, or, with
+// `norm_first`, before the rotation and times a weight per component (`q_norm`, `k_norm`: [norm_dim] each, shared by the
+// heads). The rotation pairs component j with j + rot_dim / 2, or, with `interleaved`, component 2j with 2j + 1. The rows
+// may hold queries only (`has_kv` 0: a layer that reads another layer's keys and values). One warp per (token, head): the
+// head's components stay in registers between the rotation and the norm. Value heads are copied (with their bias) as
+// they are.
 #define RN_MAX_PER_LANE 16   // head sizes up to 512
 
 template <typename T>
@@ -233,7 +236,8 @@ __global__ void __launch_bounds__(256)
 rope_norm_cache_kernel(const T* __restrict__ qkv, const T* __restrict__ bias, int qkv_stride, const int* __restrict__ tok_seq,
                        const int* __restrict__ tok_pos, const int* __restrict__ slots, const float* __restrict__ inv_freq,
                        int rot_dim, int n_heads, T* __restrict__ q_out, KvSite<T> site, int write_cache, int has_kv,
-                       int norm_dim, float eps, int n_tokens, int* err) {
+                       int norm_dim, float eps, int n_tokens, int* err, int interleaved, int norm_first,
+                       const T* __restrict__ q_norm, const T* __restrict__ k_norm) {
     grid_chain_entry();
     const int D = site.head_dim, KVH = has_kv ? site.kv_heads : 0;
     const int heads_per_token = n_heads + 2 * KVH;
@@ -254,6 +258,24 @@ rope_norm_cache_kernel(const T* __restrict__ qkv, const T* __restrict__ bias, in
     if (!dst) return;
     const T* row = qkv + (size_t)t * qkv_stride + src;
     const int half = rot_dim / 2;
+    const bool normed = !is_v && eps >= 0.f;
+    const T* gain = is_q ? q_norm : k_norm;   // the norm's weight, where it has one
+    auto raw = [&](int d) { return Num<T>::to_f(row[d]) + (bias ? Num<T>::to_f(bias[src + d]) : 0.f); };
+    float before = 1.f;   // what the norm multiplies with when it comes first
+    if (normed && norm_first) {
+        float sum = 0.f;
+        for (int d = lane; d < norm_dim; d += 32) {
+            const float v = raw(d);
+            sum = fmaf(v, v, sum);
+        }
+        before = 1.f / sqrtf(warp_sum(sum) / (float)norm_dim + eps);
+    }
+    // component d as the rotation meets it
+    auto entering = [&](int d) {
+        float v = raw(d);
+        if (normed && norm_first && d < norm_dim) v = v * before * (gain ? Num<T>::to_f(gain[d]) : 1.f);
+        return v;
+    };
     float x[RN_MAX_PER_LANE];
     float sum = 0.f;
 #pragma unroll
@@ -261,19 +283,21 @@ rope_norm_cache_kernel(const T* __restrict__ qkv, const T* __restrict__ bias, in
         const int d = lane + 32 * i;
         x[i] = 0.f;
         if (d >= D) continue;
-        float own = Num<T>::to_f(row[d]) + (bias ? Num<T>::to_f(bias[src + d]) : 0.f);
-        if (!is_v && d < rot_dim) {   // component d turns with its partner d +- rot_dim / 2
-            const int j = d < half ? d : d - half, partner = d < half ? d + half : d - half;
-            const float other = Num<T>::to_f(row[partner]) + (bias ? Num<T>::to_f(bias[src + partner]) : 0.f);
+        float own = entering(d);
+        if (!is_v && d < rot_dim) {   // component d turns with its partner
+            const bool first = interleaved ? (d & 1) == 0 : d < half;
+            const int j = interleaved ? d >> 1 : (d < half ? d : d - half);
+            const int partner = interleaved ? d ^ 1 : (d < half ? d + half : d - half);
+            const float other = entering(partner);
             float sn, cs;
             sincosf((float)pos * inv_freq[j], &sn, &cs);
-            own = d < half ? own * cs - other * sn : own * cs + other * sn;
+            own = first ? own * cs - other * sn : own * cs + other * sn;
         }
         x[i] = own;
         if (d < norm_dim) sum = fmaf(own, own, sum);
     }
     float mult = 1.f;
-    if (!is_v && eps >= 0.f) mult = rsqrtf(warp_sum(sum) / (float)norm_dim + eps);
+    if (normed && !norm_first) mult = rsqrtf(warp_sum(sum) / (float)norm_dim + eps);
 #pragma unroll
     for (int i = 0; i < RN_MAX_PER_LANE; ++i) {
         const int d = lane + 32 * i;
@@ -281,11 +305,13 @@ rope_norm_cache_kernel(const T* __restrict__ qkv, const T* __restrict__ bias, in
     }
 }
 
-QF_EXPORT int qf_rope_norm_cache_write(int is_bf16, const void* qkv, const void* bias, int qkv_stride, const int* tok_seq,
-                                       const int* tok_pos, const int* slots, const float* inv_freq, int rot_dim, int n_heads,
-                                       void* q_out, void* base, const int* table, long long page_elems, int table_stride,
-                                       int kv_heads, int head_dim, int write_cache, int has_kv, int norm_dim, float eps,
-                                       int n_tokens, int* err, cudaStream_t stream) {
+// q_norm, k_norm: the weights of a norm that comes first ([norm_dim], activation dtype), or null.
+QF_EXPORT int qf_rope_norm_cache_write_ex(int is_bf16, const void* qkv, const void* bias, int qkv_stride, const int* tok_seq,
+                                          const int* tok_pos, const int* slots, const float* inv_freq, int rot_dim, int n_heads,
+                                          void* q_out, void* base, const int* table, long long page_elems, int table_stride,
+                                          int kv_heads, int head_dim, int write_cache, int has_kv, int norm_dim, float eps,
+                                          int n_tokens, int* err, int interleaved, int norm_first, const void* q_norm,
+                                          const void* k_norm, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (!inv_freq) rot_dim = 0;
     if (rot_dim < 0 || rot_dim > head_dim || (rot_dim & 1) || head_dim > 32 * RN_MAX_PER_LANE || norm_dim <= 0 || norm_dim > head_dim)
@@ -296,11 +322,73 @@ QF_EXPORT int qf_rope_norm_cache_write(int is_bf16, const void* qkv, const void*
         return (int)launch_pdl(rope_norm_cache_kernel<bf16>, grid, block, 0, stream, (const bf16*)qkv, (const bf16*)bias, qkv_stride,
                                tok_seq, tok_pos, slots, inv_freq, rot_dim, n_heads, (bf16*)q_out,
                                KvSite<bf16>{(bf16*)base, table, page_elems, table_stride, kv_heads, head_dim}, write_cache, has_kv,
-                               norm_dim, eps, n_tokens, err);
+                               norm_dim, eps, n_tokens, err, interleaved, norm_first, (const bf16*)q_norm, (const bf16*)k_norm);
     return (int)launch_pdl(rope_norm_cache_kernel<float>, grid, block, 0, stream, (const float*)qkv, (const float*)bias, qkv_stride,
                            tok_seq, tok_pos, slots, inv_freq, rot_dim, n_heads, (float*)q_out,
                            KvSite<float>{(float*)base, table, page_elems, table_stride, kv_heads, head_dim}, write_cache, has_kv,
-                           norm_dim, eps, n_tokens, err);
+                           norm_dim, eps, n_tokens, err, interleaved, norm_first, (const float*)q_norm, (const float*)k_norm);
+}
+
+QF_EXPORT int qf_rope_norm_cache_write(int is_bf16, const void* qkv, const void* bias, int qkv_stride, const int* tok_seq,
+                                       const int* tok_pos, const int* slots, const float* inv_freq, int rot_dim, int n_heads,
+                                       void* q_out, void* base, const int* table, long long page_elems, int table_stride,
+                                       int kv_heads, int head_dim, int write_cache, int has_kv, int norm_dim, float eps,
+                                       int n_tokens, int* err, cudaStream_t stream) {
+    return qf_rope_norm_cache_write_ex(is_bf16, qkv, bias, qkv_stride, tok_seq, tok_pos, slots, inv_freq, rot_dim, n_heads, q_out,
+                                       base, table, page_elems, table_stride, kv_heads, head_dim, write_cache, has_kv, norm_dim,
+                                       eps, n_tokens, err, 0, 0, nullptr, nullptr, stream);
+}
+
+// Rows of whole blocks beside a cache: once the last position of a block of `pool` positions has been written, the block's
+// row in a second cache (`rows`: one row per block, addressed like positions) becomes the mean of the block's keys and the
+// mean of its values AS THE CACHE HOLDS THEM (float32 sums in rising order of the positions, divided by `pool`, rounded to
+// the cache's type). A block of threads per (candidate block of the step, sequence): a step of q tokens that starts at
+// position p completes the blocks floor(p / pool) .. floor((p + q) / pool) - 1.
+template <typename T>
+__global__ void __launch_bounds__(128)
+pool_cache_kernel(const int* __restrict__ cu_q, const int* __restrict__ tok_pos, const int* __restrict__ slots, KvSite<T> site,
+                  KvSite<T> rows, int pool, int* err) {
+    grid_chain_entry();
+    const int seq = blockIdx.y, slot = slots[seq];
+    if (slot < 0) return;
+    const int begin = cu_q[seq], len = cu_q[seq + 1] - begin;
+    if (len <= 0) return;
+    const int start = tok_pos[begin];
+    const int b = start / pool + blockIdx.x;
+    if ((long long)(b + 1) * pool > (long long)start + len) return;   // not complete after this step
+    const int D = site.head_dim, per_plane = site.kv_heads * D;
+    for (int i = threadIdx.x; i < 2 * per_plane; i += blockDim.x) {
+        const int which = i / per_plane, h = (i % per_plane) / D, d = i % D;
+        float sum = 0.f;
+        bool held = true;
+        for (int j = 0; j < pool; ++j) {
+            const T* src = kv_row(site, slot, b * pool + j, h, which);
+            if (src) sum += Num<T>::to_f(src[d]);
+            else held = false;
+        }
+        T* dst = kv_row(rows, slot, b, h, which);
+        if (dst && held) dst[d] = Num<T>::from_f(sum / (float)pool);
+        else if (d == 0) atomicOr(err, QF_ERR_NO_PAGE);
+    }
+}
+
+// max_blocks: the most blocks any sequence of the step can complete (max_q_len / pool + 1).
+QF_EXPORT int qf_pool_cache_write(int is_bf16, const int* cu_q, const int* tok_pos, const int* slots, int n_seqs, void* base,
+                                  const int* table, long long page_elems, int table_stride, void* rows_base, const int* rows_table,
+                                  long long rows_page_elems, int rows_table_stride, int kv_heads, int head_dim, int pool,
+                                  int max_blocks, int* err, cudaStream_t stream) {
+    if (n_seqs <= 0 || max_blocks <= 0) return 0;
+    if (pool <= 0) return (int)cudaErrorInvalidValue;
+    const dim3 grid(max_blocks, n_seqs), block(128);
+    if (is_bf16)
+        return (int)launch_pdl(pool_cache_kernel<bf16>, grid, block, 0, stream, cu_q, tok_pos, slots,
+                               KvSite<bf16>{(bf16*)base, table, page_elems, table_stride, kv_heads, head_dim},
+                               KvSite<bf16>{(bf16*)rows_base, rows_table, rows_page_elems, rows_table_stride, kv_heads, head_dim},
+                               pool, err);
+    return (int)launch_pdl(pool_cache_kernel<float>, grid, block, 0, stream, cu_q, tok_pos, slots,
+                           KvSite<float>{(float*)base, table, page_elems, table_stride, kv_heads, head_dim},
+                           KvSite<float>{(float*)rows_base, rows_table, rows_page_elems, rows_table_stride, kv_heads, head_dim},
+                           pool, err);
 }
 
 // The rotation angles of a step, once for all its layers: table[t][j] = (cos, sin) of tok_pos[t] * inv_freq[j], float32,

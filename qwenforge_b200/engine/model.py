@@ -17,7 +17,7 @@ from ..cache import SequenceCache
 from ..config import ModelConfig, ModelSpec, load_config, resolve_dtype
 from ..csrc import prepare
 from ..parts import build_block, build_part
-from ..parts.base import PendingNormed
+from ..parts.base import Pending, PendingNormed
 from ..weights import load_weights, random_state_on_device
 from .step import StepContext, context_of, pack_step
 
@@ -37,6 +37,7 @@ class Model:
         self.attention = attention
         self.embedding = build_part("embedding", spec.embedding)
         self.blocks = [build_block(layer) for layer in spec.layers]
+        self.stream_parts = [build_part("stream", part) for part in spec.stream_parts]
         self.final_norm = build_part("norm", spec.final_norm)
         self.head = build_part("head", spec.head)
         self.err = None
@@ -50,7 +51,7 @@ class Model:
 
     # ------------------------------------------------------------------ structure
     def parts(self):
-        for top in (self.embedding, *self.blocks, self.final_norm, self.head):
+        for top in (self.embedding, *self.stream_parts, *self.blocks, self.final_norm, self.head):
             yield from _walk(top)
 
     def tensor_specs(self):
@@ -66,6 +67,7 @@ class Model:
         def of(top):
             return sum(t.numel() * t.element_size() for part in _walk(top) for t in part.step_weights())
         total = of(self.embedding) + of(self.final_norm) + of(self.head)
+        total += sum(of(self.stream_parts[entry.enter]) for entry in self.spec.schedule if entry.enter is not None)
         return total + sum(of(self.blocks[entry.layer]) for entry in self.spec.schedule)
 
     def cache_needs(self) -> list:
@@ -128,21 +130,29 @@ class Model:
         ctx.step_memo = {}
         hidden = ctx.embedded if ctx.embedded is not None else self.embedding.forward(ctx.token_ids, ctx)
         delta = None
+        # the embedding's output as it is, for stream parts that mix it in again later (the stream itself is updated in place)
+        first = hidden.clone() if self.stream_parts else None
         if self.observer is not None:
             self.observer(0, hidden, None)
         for index, entry in enumerate(self.spec.schedule):
             own = entry.cache_from is None
             site = cache.site(index if own else entry.cache_from)
             block = self.blocks[entry.layer]
-            if isinstance(delta, PendingNormed) and not getattr(block, "accepts_pending_normed", False):
+            if entry.enter is not None:   # the stream passes through a part of its own before this run
+                if first is None:
+                    raise RuntimeError("a schedule entry enters through a stream part, but the embedding's output was not kept")
+                hidden = self.stream_parts[entry.enter].forward(hidden, delta, first, ctx)
+                delta = None
+            if isinstance(delta, Pending) and not (isinstance(delta, PendingNormed) and getattr(block, "accepts_pending_normed", False)) \
+                    and not isinstance(delta, getattr(block, "accepts_pending", ())):
                 delta.add_to(hidden)
                 delta = None
             delta = block.forward(hidden, delta, ctx, site, own)
             if self.observer is not None:
-                self.observer(index + 1, hidden, delta.value() if isinstance(delta, PendingNormed) else delta)
+                self.observer(index + 1, hidden, delta.value() if isinstance(delta, Pending) else delta)
         if ctx.want_rows is None:
             return None
-        if isinstance(delta, PendingNormed):
+        if isinstance(delta, Pending):
             delta.add_to(hidden)
             delta = None
         shape = (ctx.want_rows.numel(), hidden.shape[1])

@@ -204,12 +204,18 @@ def gemm_f32(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]
 def rope_cache_write(qkv: torch.Tensor, tok_seq: torch.Tensor, tok_pos: torch.Tensor, slots: torch.Tensor,
                      inv_freq: Optional[torch.Tensor], rot_dim: int, n_heads: int, q_out: torch.Tensor,
                      site: KvSiteArgs, write_cache: bool, err: torch.Tensor, bias: Optional[torch.Tensor] = None,
-                     unit_norm_eps: Optional[float] = None, norm_dim: int = 0, has_kv: bool = True) -> None:
+                     unit_norm_eps: Optional[float] = None, norm_dim: int = 0, has_kv: bool = True,
+                     interleaved: bool = False, norm_first: bool = False, q_norm: Optional[torch.Tensor] = None,
+                     k_norm: Optional[torch.Tensor] = None) -> None:
     """Rotate q and k heads of qkv [T, (NH + 2 KVH) D] by position, write q to q_out [T, NH D] and k, v into the cache.
+    The rows of qkv may be the first columns of wider rows (unit inner stride).
     `unit_norm_eps`: after the rotation every q and k head is divided by its root mean square (float32), the mean taken
     over the head's first `norm_dim` components (0: all; a head padded with zeros beyond its own size names that size).
+    `norm_first`: that division comes before the rotation instead, and `q_norm` / `k_norm` ([norm_dim], shared by the
+    heads) then multiply the components. `interleaved`: the rotation pairs component 2j with 2j + 1 instead of j with
+    j + rot_dim / 2.
     `has_kv` false: the rows hold queries only, [T, NH D] (a layer that reads another layer's keys and values)."""
-    _dev("qkv", qkv)
+    _rows("qkv", qkv)
     _dev("q_out", q_out, qkv.dtype)
     _dev("cache", site.storage, qkv.dtype)
     _dev("tok_seq", tok_seq, torch.int32)
@@ -217,28 +223,36 @@ def rope_cache_write(qkv: torch.Tensor, tok_seq: torch.Tensor, tok_pos: torch.Te
     _dev("slots", slots, torch.int32)
     n = qkv.shape[0]
     d, kvh = site.head_dim, site.kv_heads
-    if qkv.shape[1] != (n_heads + (2 * kvh if has_kv else 0)) * d or q_out.shape != (n, n_heads * d):
+    if qkv.shape[1] < (n_heads + (2 * kvh if has_kv else 0)) * d or q_out.shape != (n, n_heads * d):
         raise KernelError("rope_cache_write: qkv/q_out widths do not match the head counts")
     if not has_kv and write_cache:
         raise KernelError("rope_cache_write: rows without keys and values cannot write a cache")
     if bias is not None:
         _dev("bias", bias, qkv.dtype)
-        if bias.numel() != qkv.shape[1]:
+        if bias.numel() != (n_heads + (2 * kvh if has_kv else 0)) * d:
             raise KernelError("rope_cache_write: bias must have one element per projection column")
     if inv_freq is not None:
         _dev("inv_freq", inv_freq, torch.float32)
         if inv_freq.numel() * 2 != rot_dim:
             raise KernelError("rope_cache_write: inv_freq must hold rot_dim / 2 frequencies")
-    if unit_norm_eps is not None or not has_kv:
+    if unit_norm_eps is not None or not has_kv or interleaved:
         if not 0 <= norm_dim <= d:
             raise KernelError("rope_cache_write: norm_dim must lie within the head size")
-        _check(library("rope_cache").qf_rope_norm_cache_write(
+        for name, w in (("q_norm", q_norm), ("k_norm", k_norm)):
+            if w is not None:
+                _dev(name, w, qkv.dtype)
+                if not norm_first or unit_norm_eps is None or w.numel() != (norm_dim or d):
+                    raise KernelError(f"rope_cache_write: {name} goes with a norm before the rotation and holds norm_dim weights")
+        _check(library("rope_cache").qf_rope_norm_cache_write_ex(
             _I(_is_bf16(qkv.dtype)), _ptr(qkv), _ptr(bias), _I(qkv.stride(0)), _ptr(tok_seq), _ptr(tok_pos), _ptr(slots),
             _ptr(inv_freq), _I(rot_dim), _I(n_heads), _ptr(q_out), _ptr(site.storage), _ptr(site.table),
             _LL(site.page_elems), _I(site.table_stride), _I(kvh), _I(d), _I(1 if write_cache else 0), _I(1 if has_kv else 0),
-            _I(norm_dim or d), _F(-1.0 if unit_norm_eps is None else unit_norm_eps), _I(n), _ptr(err), _stream()),
+            _I(norm_dim or d), _F(-1.0 if unit_norm_eps is None else unit_norm_eps), _I(n), _ptr(err), _I(int(interleaved)),
+            _I(int(norm_first)), _ptr(q_norm), _ptr(k_norm), _stream()),
             "rope_cache_write")
         return
+    if norm_first or q_norm is not None or k_norm is not None:
+        raise KernelError("rope_cache_write: a norm before the rotation needs its eps (unit_norm_eps)")
     _check(library("rope_cache").qf_rope_cache_write(
         _I(_is_bf16(qkv.dtype)), _ptr(qkv), _ptr(bias), _I(qkv.stride(0)), _ptr(tok_seq), _ptr(tok_pos), _ptr(slots),
         _ptr(inv_freq), _I(rot_dim), _I(n_heads), _ptr(q_out), _ptr(site.storage), _ptr(site.table),
@@ -254,8 +268,11 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, to
                       slots: torch.Tensor, site: KvSiteArgs, n_heads: int, n_seqs: int, max_q_len: int, scale: float,
                       window: int, err: torch.Tensor, scratch: Optional["DecodeScratch"] = None,
                       max_kv_len: Optional[int] = None, sinks: Optional[torch.Tensor] = None,
-                      shared_values: bool = False, chunk: int = 0, softcap: float = 0.0) -> None:
+                      shared_values: bool = False, chunk: int = 0, softcap: float = 0.0,
+                      blocks: Optional[KvSiteArgs] = None, pool: int = 0) -> None:
     """Causal grouped-query attention of the step's queries over each sequence's cache (any sizes, SIMT float32 math).
+    `pool` > 0 with `blocks` (a second cache of the same head shape that holds one row per block of `pool` positions) and a
+    window: a query also sees the row of every block that lies wholly before its window, in the same softmax.
     `chunk` > 0: a query sees only the keys of its own block of `chunk` positions (blocks counted from position 0 of the
     sequence). `softcap` > 0: a score s (after the scale) becomes softcap * tanh(s / softcap).
     `sinks` (float32 [n_heads]): a logit per head that joins the softmax's denominator once, with no key and no value.
@@ -275,7 +292,11 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, to
         _dev("sinks", sinks, torch.float32)
         if sinks.numel() != n_heads:
             raise KernelError("attention_generic: sinks must hold one float32 per query head")
-    if (scratch is not None and max_kv_len is not None and max_q_len == 1 and q.shape[0] == n_seqs
+    if pool > 0:
+        if blocks is None or window <= 0 or shared_values or (blocks.kv_heads, blocks.head_dim) != (site.kv_heads, d):
+            raise KernelError("attention_generic: rows of whole blocks need a window and a second cache of the same head shape")
+        _dev("block rows", blocks.storage, q.dtype)
+    elif (scratch is not None and max_kv_len is not None and max_q_len == 1 and q.shape[0] == n_seqs
             and max_kv_len > GENERIC_DECODE_CHUNK):
         n_chunks = -(-int(max_kv_len) // GENERIC_DECODE_CHUNK)
         scratch.ensure(n_seqs, n_heads, n_chunks, d, 0)
@@ -285,11 +306,13 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, to
             _I(n_seqs), _I(int(max_kv_len)), _F(scale), _I(window), _ptr(scratch.part_o), _ptr(scratch.part_ml), _ptr(err),
             _ptr(sinks), _I(int(bool(shared_values))), _I(int(chunk)), _F(softcap), _stream()), "attention_generic")
         return
-    _check(library("attention_generic").qf_attention_generic_masked(
+    _check(library("attention_generic").qf_attention_generic_pooled(
         _I(_is_bf16(q.dtype)), _ptr(q), _ptr(out), _ptr(cu_q), _ptr(tok_pos), _ptr(slots), _ptr(site.storage),
         _ptr(site.table), _LL(site.page_elems), _I(site.table_stride), _I(site.kv_heads), _I(d), _I(n_heads),
         _I(n_seqs), _I(max_q_len), _F(scale), _I(window), _ptr(err), _ptr(sinks), _I(int(bool(shared_values))),
-        _I(int(chunk)), _F(softcap), _stream()), "attention_generic")
+        _I(int(chunk)), _F(softcap), _ptr(blocks.storage if pool > 0 else None), _ptr(blocks.table if pool > 0 else None),
+        _LL(blocks.page_elems if pool > 0 else 0), _I(blocks.table_stride if pool > 0 else 0), _I(int(pool)), _stream()),
+        "attention_generic")
 
 
 FAST_ATTENTION_HEAD_DIMS = (32, 64, 96, 128)
@@ -906,6 +929,89 @@ def residual_add(hidden: torch.Tensor, delta: torch.Tensor) -> None:
 TC_PLAIN, TC_SWIGLU = 0, 1
 
 
+def add_dyt_norm(hidden: torch.Tensor, a: Optional[torch.Tensor], b: Optional[torch.Tensor], weight: torch.Tensor,
+                 bias: torch.Tensor, alpha: float, out: torch.Tensor) -> None:
+    """hidden += (a + b) (each if given); out = tanh(alpha * hidden) * weight + bias: Dynamic Tanh in a norm's place, element by
+    element, float32 inside. hidden float32 [R, W]; a, b, weight, bias, out share the activation dtype."""
+    _dev("hidden", hidden, torch.float32)
+    _dev("weight", weight)
+    _dev("bias", bias, weight.dtype)
+    _dev("out", out, weight.dtype)
+    rows, width = hidden.shape
+    if weight.shape != (width,) or bias.shape != (width,) or out.shape != hidden.shape:
+        raise KernelError("add_dyt_norm: weight and bias must be [width], out must have hidden's shape")
+    for name, t in (("a", a), ("b", b)):
+        if t is not None:
+            _dev(name, t, weight.dtype)
+            if t.shape != hidden.shape:
+                raise KernelError(f"add_dyt_norm: {name} and hidden differ in shape")
+    _check(library("norm").qf_add_dyt_norm(_I(_is_bf16(weight.dtype)), _ptr(hidden), _ptr(a), _ptr(b), _ptr(weight), _ptr(bias),
+                                           _F(alpha), _ptr(out), _I(rows), _I(width), _stream()), "add_dyt_norm")
+
+
+def residual_add_pair(hidden: torch.Tensor, a: Optional[torch.Tensor], b: Optional[torch.Tensor]) -> None:
+    """hidden += (a + b): the two pending outputs of one layer, summed with each other first (float32)."""
+    _dev("hidden", hidden, torch.float32)
+    first = a if a is not None else b
+    if first is None:
+        return
+    for name, t in (("a", a), ("b", b)):
+        if t is not None:
+            _dev(name, t, first.dtype)
+            if t.shape != hidden.shape:
+                raise KernelError(f"residual_add_pair: {name} and hidden differ in shape")
+    _check(library("norm").qf_residual_add_pair(_I(_is_bf16(first.dtype)), _ptr(hidden), _ptr(a), _ptr(b), _LL(hidden.numel()),
+                                                _stream()), "residual_add_pair")
+
+
+def stream_pair(hidden: torch.Tensor, a: Optional[torch.Tensor], b: Optional[torch.Tensor], other: torch.Tensor,
+                out: torch.Tensor) -> None:
+    """out[t] = [hidden[t] + (a[t] + b[t]) | other[t]] in out's dtype: two float32 streams side by side as a product's
+    input; a, b are pending outputs (each if given, of out's dtype); hidden is not changed."""
+    _dev("hidden", hidden, torch.float32)
+    _dev("other", other, torch.float32)
+    _dev("out", out)
+    rows, width = hidden.shape
+    if other.shape != hidden.shape or out.shape != (rows, 2 * width):
+        raise KernelError("stream_pair: other must have hidden's shape, out twice its width")
+    for name, t in (("a", a), ("b", b)):
+        if t is not None:
+            _dev(name, t, out.dtype)
+            if t.shape != hidden.shape:
+                raise KernelError(f"stream_pair: {name} and hidden differ in shape")
+    _check(library("norm").qf_stream_pair(_I(_is_bf16(out.dtype)), _ptr(hidden), _ptr(a), _ptr(b), _ptr(other), _ptr(out), _I(rows),
+                                          _I(width), _stream()), "stream_pair")
+
+
+def head_gate(x: torch.Tensor, gate: torch.Tensor, n_heads: int) -> None:
+    """x[t, h, :] *= sigmoid(gate[t, h]) in place: x [T, n_heads * D]; gate [T, n_heads], which may be columns of wider rows."""
+    _dev("x", x)
+    _rows("gate", gate, x.dtype)
+    rows, width = x.shape
+    if width % n_heads or gate.shape != (rows, n_heads):
+        raise KernelError("head_gate: x must be [T, n_heads * D] and gate [T, n_heads]")
+    _check(library("activation").qf_head_gate(_I(_is_bf16(x.dtype)), _ptr(x), _ptr(gate), _I(gate.stride(0)), _I(rows), _I(n_heads),
+                                              _I(width // n_heads), _stream()), "head_gate")
+
+
+def pool_cache_write(cu_q: torch.Tensor, tok_pos: torch.Tensor, slots: torch.Tensor, site: KvSiteArgs, blocks: KvSiteArgs,
+                     pool: int, max_q_len: int, err: torch.Tensor) -> None:
+    """For every block of `pool` positions that this step completed (its last position is among the step's tokens, whose
+    keys and values are in the cache already): row b of `blocks` <- the mean of the block's keys and the mean of its values
+    as `site` holds them (float32 sums, rounded to the cache's dtype)."""
+    for name, t in (("cu_q", cu_q), ("tok_pos", tok_pos), ("slots", slots)):
+        _dev(name, t, torch.int32)
+    _dev("cache", site.storage)
+    _dev("block rows", blocks.storage, site.storage.dtype)
+    if pool <= 0 or (blocks.kv_heads, blocks.head_dim) != (site.kv_heads, site.head_dim):
+        raise KernelError("pool_cache_write: pool must be positive and both caches of one head shape")
+    _check(library("rope_cache").qf_pool_cache_write(
+        _I(_is_bf16(site.storage.dtype)), _ptr(cu_q), _ptr(tok_pos), _ptr(slots), _I(slots.numel()), _ptr(site.storage),
+        _ptr(site.table), _LL(site.page_elems), _I(site.table_stride), _ptr(blocks.storage), _ptr(blocks.table),
+        _LL(blocks.page_elems), _I(blocks.table_stride), _I(site.kv_heads), _I(site.head_dim), _I(int(pool)),
+        _I(int(max_q_len) // int(pool) + 1), _ptr(err), _stream()), "pool_cache_write")
+
+
 def tc_gemm_takes(x: torch.Tensor, weight: torch.Tensor) -> bool:
     """Whether the tcgen05 kernel takes x [M, K] against weight [N, K]: bf16, K and the row strides multiples of 8."""
     return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.stride(1) == 1 and weight.stride(1) == 1
@@ -1162,11 +1268,14 @@ def moe_tile_rows(n_tokens: int, n_experts: int, top: int, weight: torch.Tensor)
 
 
 def moe_plan(logits: Optional[torch.Tensor], top: int, softmax_scores: bool = False, renormalize: bool = False,
-             tile_rows: int = GROUP_TILE_ROWS, x: Optional[torch.Tensor] = None, router: Optional[torch.Tensor] = None) -> MoePlan:
+             tile_rows: int = GROUP_TILE_ROWS, x: Optional[torch.Tensor] = None, router: Optional[torch.Tensor] = None,
+             bias: Optional[torch.Tensor] = None) -> MoePlan:
     """Route: logits float32 [T, E] -> the `top` experts with the largest scores per token (sigmoid of the logit, or the
     softmax over the experts) and the sorted rows (see `MoePlan`), cut into tiles of `tile_rows`. Everything stays on the
     device. With `logits` None, the kernel makes the logits itself from `x` [T, W] and `router` [E, W] (float32 sums; for
-    steps of few tokens, T * E <= MOE_FUSED_ROUTER_MAX)."""
+    steps of few tokens, T * E <= MOE_FUSED_ROUTER_MAX). `bias` (float32 [E]) is added to the logits before the choice."""
+    if bias is not None:
+        _dev("bias", bias, torch.float32)
     if logits is not None:
         _dev("logits", logits, torch.float32)
         n_tokens, n_experts = logits.shape
@@ -1177,24 +1286,26 @@ def moe_plan(logits: Optional[torch.Tensor], top: int, softmax_scores: bool = Fa
         (n_tokens, width), n_experts = x.shape, router.shape[0]
         if router.shape[1] != width or n_tokens * n_experts > MOE_FUSED_ROUTER_MAX:
             raise KernelError("moe_plan: x [T, W] and router [E, W] with T * E <= %d, or give the logits" % MOE_FUSED_ROUTER_MAX)
+    if bias is not None and bias.numel() != n_experts:
+        raise KernelError("moe_plan: bias must hold one float32 per expert")
     plan = MoePlan(n_tokens, n_experts, top, (logits if logits is not None else x).device, tile_rows)
     if logits is not None and n_tokens >= MOE_LONG_PLAN_TOKENS and n_experts <= 4096:
         expert_rows = torch.zeros(n_experts, dtype=torch.int32, device=logits.device)
-        code = library("moe").qf_moe_plan_long(
+        code = library("moe").qf_moe_plan_long_biased(
             _ptr(logits), _I(n_tokens), _I(n_experts), _I(top), _I(int(softmax_scores)), _I(int(renormalize)),
             _ptr(plan.pair_expert), _ptr(plan.pair_weight), _ptr(plan.sorted_token), _ptr(plan.sorted_weight), _ptr(plan.dest),
             _ptr(plan.offsets), _ptr(plan.tile_group), _ptr(plan.tile_row0), _ptr(plan.n_tiles), _I(plan.max_tiles),
-            _I(tile_rows), _ptr(expert_rows), _stream())
+            _I(tile_rows), _ptr(expert_rows), _ptr(bias), _stream())
         if code == 1:
             raise KernelError(f"moe_plan: {top} of {n_experts} experts is not supported (top <= 16)")
         _check(code, "moe_plan")
         return plan
-    code = library("moe").qf_moe_plan(_ptr(logits), _I(n_tokens), _I(n_experts), _I(top), _I(int(softmax_scores)),
+    code = library("moe").qf_moe_plan_biased(_ptr(logits), _I(n_tokens), _I(n_experts), _I(top), _I(int(softmax_scores)),
                                       _I(int(renormalize)), _ptr(plan.pair_expert), _ptr(plan.pair_weight),
                                       _ptr(plan.sorted_token), _ptr(plan.sorted_weight), _ptr(plan.dest), _ptr(plan.offsets),
                                       _ptr(plan.tile_group), _ptr(plan.tile_row0), _ptr(plan.n_tiles), _I(plan.max_tiles),
                                       _I(tile_rows), _ptr(x if logits is None else None), _ptr(router if logits is None else None),
-                                      _I(width), _I(_is_bf16(x.dtype) if logits is None else 0), _stream())
+                                      _I(width), _I(_is_bf16(x.dtype) if logits is None else 0), _ptr(bias), _stream())
     if code == 1:
         raise KernelError(f"moe_plan: {top} of {n_experts} experts is not supported (top <= 16, experts <= 8192)")
     _check(code, "moe_plan")
@@ -1211,16 +1322,26 @@ def moe_gather(x: torch.Tensor, plan: MoePlan, out: torch.Tensor, scale_input: b
                                         _ptr(out), _I(plan.pairs), _I(x.shape[1]), _I(int(scale_input)), _stream()), "moe_gather")
 
 
-def moe_combine(y: torch.Tensor, plan: MoePlan, out: torch.Tensor, scale_output: bool) -> None:
+def moe_combine(y: torch.Tensor, plan: MoePlan, out: torch.Tensor, scale_output: bool, extra: Optional[torch.Tensor] = None,
+                extra_gate: Optional[torch.Tensor] = None) -> None:
     """out[t] = the sum over token t's choices, in their order, of y[row of the choice] (times the routing weight with
-    `scale_output`), summed in float32; y [T * top, W], out [T, W]."""
+    `scale_output`), summed in float32; y [T * top, W], out [T, W]. `extra` [T, W] is an output that every token gets beside
+    its chosen ones; it is added times sigmoid(extra_gate[t]) where `extra_gate` (float32, one logit per token) is given."""
     _dev("y", y)
     _dev("out", out, y.dtype)
     if y.shape[0] != plan.pairs or out.shape != (plan.n_tokens, y.shape[1]):
         raise KernelError("moe_combine: y must be [tokens * top, width], out [tokens, width]")
-    _check(library("moe").qf_moe_combine(_I(_is_bf16(y.dtype)), _ptr(y), _ptr(plan.dest), _ptr(plan.sorted_weight), _ptr(out),
-                                         _I(plan.n_tokens), _I(plan.top), _I(y.shape[1]), _I(int(scale_output)), _stream()),
-           "moe_combine")
+    if extra is not None:
+        _dev("extra", extra, y.dtype)
+        if extra.shape != out.shape:
+            raise KernelError("moe_combine: extra must have out's shape")
+    if extra_gate is not None:
+        _dev("extra_gate", extra_gate, torch.float32)
+        if extra is None or extra_gate.numel() != plan.n_tokens:
+            raise KernelError("moe_combine: extra_gate holds one float32 per token and goes with extra")
+    _check(library("moe").qf_moe_combine_shared(_I(_is_bf16(y.dtype)), _ptr(y), _ptr(plan.dest), _ptr(plan.sorted_weight), _ptr(out),
+                                                _I(plan.n_tokens), _I(plan.top), _I(y.shape[1]), _I(int(scale_output)), _ptr(extra),
+                                                _ptr(extra_gate), _stream()), "moe_combine")
 
 
 def expert_linear(x: torch.Tensor, weight: torch.Tensor, plan: MoePlan, out: torch.Tensor, gather: bool = False) -> None:
@@ -1316,11 +1437,11 @@ def tc_gemm_grouped(epilogue: int, x: torch.Tensor, weight: torch.Tensor, plan: 
 
 # ---------------------------------------------------------------------------------------------------------------------
 # Elementwise kernels of feed-forwards with a bias and of capped logits (csrc/activation.cu)
-ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2, "relu": 3, "gelu": 4}
 
 
 def bias_act(x: torch.Tensor, bias: Optional[torch.Tensor], kind: str, out: torch.Tensor) -> None:
-    """out = act(x + bias), float32 inside. kind: relu2 (the square of relu), gelu_tanh, silu, relu."""
+    """out = act(x + bias), float32 inside. kind: relu2 (the square of relu), gelu_tanh, gelu (the exact form, through erf), silu, relu."""
     _dev("x", x)
     _dev("out", out, x.dtype)
     if kind not in ACTIVATIONS:
@@ -1489,8 +1610,10 @@ CONV_MAX_TAPS = 16
 
 
 def causal_conv_silu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], cu_q: torch.Tensor,
-                     tok_seq: torch.Tensor, slots: torch.Tensor, state: torch.Tensor, offset: int, out: torch.Tensor) -> None:
-    """A causal convolution per channel over each sequence's tokens, then silu: out[t, c] = silu(b[c] + sum_j w[c, j] *
+                     tok_seq: torch.Tensor, slots: torch.Tensor, state: torch.Tensor, offset: int, out: torch.Tensor,
+                     activation: str = "silu") -> None:
+    """A causal convolution per channel over each sequence's tokens, then silu (`activation` "none": the convolution
+    alone): out[t, c] = silu(b[c] + sum_j w[c, j] *
     x[t - (taps - 1 - j), c]); inputs before the step's first token come from `state` (the sequence's last taps - 1 inputs,
     float32 [taps - 1, C] at `offset`, zeros at a sequence's start), which then takes the step's last taps - 1 inputs.
     x: [T, C] in the activation dtype (rows may be strided); weight [C, taps], bias [C] float32; out [T, C]."""
@@ -1507,7 +1630,14 @@ def causal_conv_silu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch
         if bias.numel() != c:
             raise KernelError("causal_conv_silu: bias must hold one float32 per channel")
     _state(state, (offset, (taps - 1) * c))
-    _check(library("recurrent").qf_causal_conv_silu(
+    if activation not in ("silu", "none"):
+        raise KernelError(f"causal_conv_silu: activation {activation!r} is not known ('silu' or 'none')")
+    _check(library("recurrent").qf_causal_conv(
         _I(_is_bf16(x.dtype)), _ptr(x), _I(x.stride(0)), _ptr(weight), _ptr(bias), _ptr(cu_q), _ptr(tok_seq), _ptr(slots),
-        _I(cu_q.numel() - 1), _ptr(state), _LL(state.stride(0)), _LL(offset), _I(taps), _I(n), _I(c), _ptr(out), _stream()),
-        "causal_conv_silu")
+        _I(cu_q.numel() - 1), _ptr(state), _LL(state.stride(0)), _LL(offset), _I(taps), _I(n), _I(c), _ptr(out),
+        _I(1 if activation == "none" else 0), _stream()), "causal_conv_silu")
+
+
+def causal_conv(x, weight, bias, cu_q, tok_seq, slots, state, offset, out) -> None:
+    """`causal_conv_silu` without the activation."""
+    causal_conv_silu(x, weight, bias, cu_q, tok_seq, slots, state, offset, out, activation="none")

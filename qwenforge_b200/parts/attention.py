@@ -20,13 +20,25 @@ Options that other designs switch on, each a parameter of the spec (all off for 
   chunk          key j is visible to query i only inside i's block of `chunk` positions (counted from position 0)
   sink           "unit": one more term exp(0) in the softmax's denominator, with no value
   own_kv         false: no key and value projections; the layer reads the cache of the schedule entry it is pointed at
+  conv_taps      a short causal convolution over time on every channel of q, k and v, right after the projection
+                 (y_t = sum_j c[:, j] u_(t - taps + 1 + j), no bias, zeros before a sequence's start); the last taps - 1
+                 projected rows of a sequence are part of its state
+  qk_norm_eps    q and k are RMS-normed per head BEFORE the rotation, with a weight each (`q_norm`, `k_norm`: [head_dim],
+                 shared by the heads)
+  sink           "learned": exp(sink_h) joins the softmax's denominator, a number per head from the weight files
+  pool           with a window: one pooled key and value for every block of `pool` positions that lies wholly before the
+                 query's window (block b is seen from position b * pool + pool - 1 + window on), the means of the block's
+                 keys and values as the cache holds them, in the same softmax. They live in a second paged cache of one row
+                 per block; the positions themselves stay until their block is complete
+  head_gate      every head's output is multiplied by sigmoid(G h)_head, one more projection [heads, hidden] of the same input
+The position part may pair components 2j and 2j + 1 (`rotary_interleaved`) instead of j and j + R/2.
 """
 from __future__ import annotations
 
 import torch
 
 from .. import ops
-from ..cache import PAGE_TOKENS, KvNeed
+from ..cache import PAGE_TOKENS, BundleNeed, KvNeed, StateNeed
 from .base import Mixer, TensorSpec
 from .registry import build_part, register_part
 
@@ -58,11 +70,24 @@ class GqaAttention(Mixer):
         self.chunk = int(p.get("chunk") or 0)
         self.sink = str(p.get("sink") or "none")
         self.own_kv = bool(p.get("own_kv", True))
-        if self.sink not in ("none", "unit"):
-            raise ValueError(f"gqa_attention: sink {self.sink!r} is not known ('none' or 'unit')")
+        self.conv_taps = int(p.get("conv_taps") or 0)
+        self.qk_norm_eps = None if p.get("qk_norm_eps") is None else float(p["qk_norm_eps"])
+        self.pool = int(p.get("pool") or 0)
+        self.gated = bool(p.get("head_gate", False))
+        if self.sink not in ("none", "unit", "learned"):
+            raise ValueError(f"gqa_attention: sink {self.sink!r} is not known ('none', 'unit' or 'learned')")
+        if self.unit_norm_eps is not None and self.qk_norm_eps is not None:
+            raise ValueError("gqa_attention: a norm of q and k comes either before the rotation (qk_norm_eps) or after it (unit_norm_eps)")
+        if self.pool > 0 and (int(p.get("window") or 0) <= 0 or self.chunk > 0 or not self.own_kv):
+            raise ValueError("gqa_attention: pooled blocks go with a window, without a block mask, in a layer with keys of its own")
+        if self.conv_taps > ops.CONV_MAX_TAPS or (self.conv_taps > 0 and (not self.own_kv or p.get("qkv_bias"))):
+            raise ValueError(f"gqa_attention: a short convolution has up to {ops.CONV_MAX_TAPS} taps and goes with q, k and v "
+                             "of the layer's own, without biases")
+        self.interleaved = bool(p.get("position") is not None and p["position"].kind == "rotary_interleaved")
         # the form that every tensor-core kernel and fused product of this part takes
         self.plain = (self.value_dim == self.key_dim and self.unit_norm_eps is None and self.softcap == 0.0 and self.chunk == 0
-                      and self.sink == "none" and self.own_kv)
+                      and self.sink == "none" and self.own_kv and self.conv_taps == 0 and self.qk_norm_eps is None
+                      and self.pool == 0 and not self.gated and not self.interleaved)
         self.qkv_bias = bool(p.get("qkv_bias", False))
         self.out_bias = bool(p.get("out_bias", False))
         self.scale = float(p.get("scale") or self.key_dim ** -0.5)
@@ -74,7 +99,9 @@ class GqaAttention(Mixer):
         self.position = build_part("position", p["position"]) if p.get("position") is not None else None
         self.q_width = self.n_heads * self.head_dim
         self.kv_width = self.n_kv * self.head_dim
+        self.qkv_width = self.q_width + (2 * self.kv_width if self.own_kv else 0)   # the gates' columns follow
         self.qkv_weight = self.qkv_bias_t = self.o_weight = self.o_bias_t = self.sinks = None
+        self.conv_weight = self.q_norm = self.k_norm = None
 
     def sub_parts(self):
         return [self.position] if self.position is not None else []
@@ -93,10 +120,21 @@ class GqaAttention(Mixer):
                           TensorSpec(self.file_name("v_bias"), (self.n_kv * vd,), init="bias")]
         if self.out_bias:
             specs.append(TensorSpec(self.file_name("o_bias"), (self.hidden,), init="bias"))
+        if self.conv_taps > 0:
+            specs += [TensorSpec(self.file_name("q_conv"), (self.n_heads * kd, self.conv_taps), init="conv", keep="float32"),
+                      TensorSpec(self.file_name("k_conv"), (self.n_kv * kd, self.conv_taps), init="conv", keep="float32"),
+                      TensorSpec(self.file_name("v_conv"), (self.n_kv * vd, self.conv_taps), init="conv", keep="float32")]
+        if self.qk_norm_eps is not None:
+            specs += [TensorSpec(self.file_name("q_norm"), (kd,), init="norm"), TensorSpec(self.file_name("k_norm"), (kd,), init="norm")]
+        if self.sink == "learned":
+            specs.append(TensorSpec(self.file_name("sink"), (self.n_heads,), init="logit", keep="float32"))
+        if self.gated:
+            specs.append(TensorSpec(self.file_name("g_weight"), (self.n_heads, self.hidden)))
         return specs
 
     def kernel_libraries(self, dtype):
-        libs = {"rope_cache", "attention_generic"}
+        libs = {"rope_cache", "attention_generic"} | ({"recurrent"} if self.conv_taps > 0 else set()) \
+            | ({"activation"} if self.gated else set())
         if dtype == torch.float32:
             libs.add("gemm_f32")
         elif not self.plain and self.head_dim in ops.FAST_ATTENTION_HEAD_DIMS:
@@ -108,7 +146,15 @@ class GqaAttention(Mixer):
         return libs
 
     def cache_need(self):
-        return KvNeed(self.n_kv, self.head_dim, self.window, chunk=self.chunk)
+        kv = KvNeed(self.n_kv, self.head_dim, self.window, chunk=self.chunk, pool=self.pool)
+        if self.pool <= 0 and self.conv_taps <= 0:
+            return kv
+        items = [("kv", kv)]
+        if self.pool > 0:
+            items.append(("blocks", KvNeed(self.n_kv, self.head_dim, every=self.pool)))
+        if self.conv_taps > 0:   # (a convolution of one tap keeps nothing; its row is never read or written)
+            items.append(("conv", StateNeed((max(self.conv_taps - 1, 1) * self.qkv_width,), torch.float32)))
+        return BundleNeed(tuple(items))
 
     def _padded(self, rows: torch.Tensor, heads: int, size: int) -> torch.Tensor:
         """Rows [heads * size, ...] of a projection (or its bias) with every head filled up with zero rows to head_dim."""
@@ -124,7 +170,14 @@ class GqaAttention(Mixer):
         pieces = [self._padded(t("q_weight"), self.n_heads, kd)]
         if self.own_kv:
             pieces += [self._padded(t("k_weight"), self.n_kv, kd), self._padded(t("v_weight"), self.n_kv, vd)]
+        if self.gated:   # the gates' logits are further columns of the one product
+            pieces.append(t("g_weight"))
         self.qkv_weight = torch.cat(pieces, dim=0).contiguous()
+        if self.conv_taps > 0:   # zero taps under the padding: what is zero stays zero
+            self.conv_weight = torch.cat((self._padded(t("q_conv"), self.n_heads, kd), self._padded(t("k_conv"), self.n_kv, kd),
+                                          self._padded(t("v_conv"), self.n_kv, vd)), dim=0).to(torch.float32).contiguous()
+        if self.qk_norm_eps is not None:
+            self.q_norm, self.k_norm = t("q_norm").contiguous(), t("k_norm").contiguous()
         if self.qkv_bias:
             pieces = [self._padded(t("q_bias"), self.n_heads, kd)]
             if self.own_kv:
@@ -138,9 +191,12 @@ class GqaAttention(Mixer):
             self.o_bias_t = t("o_bias")
         if self.sink == "unit":
             self.sinks = torch.zeros(self.n_heads, dtype=torch.float32, device=device)
+        elif self.sink == "learned":
+            self.sinks = t("sink").to(torch.float32).contiguous()
 
     def step_weights(self):
-        return [t for t in (self.qkv_weight, self.qkv_bias_t, self.o_weight, self.o_bias_t) if t is not None]
+        return [t for t in (self.qkv_weight, self.qkv_bias_t, self.o_weight, self.o_bias_t, self.conv_weight, self.q_norm,
+                            self.k_norm) if t is not None]
 
     def forward(self, x, ctx, site, writes_cache):
         n = x.shape[0]
@@ -183,22 +239,40 @@ class GqaAttention(Mixer):
         return ops.linear(attended, self.o_weight, self.o_bias_t)
 
     def _forward_with_options(self, x, ctx, site, writes_cache):
-        """The step with any of the options on: one product for what the layer projects, one kernel for bias, rotation,
-        unit norm and the cache write, then attention over the cache with the mask, the cap and the sink."""
+        """The step with any of the options on: one product for what the layer projects, the short convolution, one kernel
+        for bias, norms, rotation and the cache write, the pooled rows of the blocks that the step completed, then attention
+        over the cache with the mask, the cap, the pooled rows and the sink, the heads' gates, the output projection."""
         n = x.shape[0]
         if self.position is not None and self.position.fused_rotary() is None:
             raise ValueError("gqa_attention: the options need a position part with a fused form (or none)")
         if not self.own_kv and writes_cache:
             raise ValueError("gqa_attention: a layer without keys and values of its own must be pointed at another entry's cache")
+        bundled = self.pool > 0 or self.conv_taps > 0
+        if bundled and not writes_cache:
+            raise ValueError("gqa_attention: a layer with a convolution's state or pooled rows cannot read another entry's cache")
+        kv_site = site["kv"] if bundled else site
         inv_freq, rot_dim = self.position.fused_rotary() if self.position is not None else (None, 0)
-        qkv = ops.linear_rows(x, self.qkv_weight)
+        qkv = ops.linear_rows(x, self.qkv_weight)           # [T, q | k | v (| gates)]
+        gates = qkv[:, self.qkv_width:] if self.gated else None
+        if self.conv_taps > 0:
+            mixed = torch.empty((n, self.qkv_width), dtype=x.dtype, device=x.device)
+            ops.causal_conv(qkv[:, :self.qkv_width], self.conv_weight, None, ctx.cu_q, ctx.tok_seq, ctx.slots, site["conv"].storage,
+                            0, mixed)
+            qkv = mixed
         q = torch.empty((n, self.q_width), dtype=x.dtype, device=x.device)
-        args = ops.KvSiteArgs(site.storage, site.table, self.n_kv, self.head_dim)
+        args = ops.KvSiteArgs(kv_site.storage, kv_site.table, self.n_kv, self.head_dim)
+        norm_first = self.qk_norm_eps is not None
         ops.rope_cache_write(qkv, ctx.tok_seq, ctx.tok_pos, ctx.slots, inv_freq, rot_dim, self.n_heads, q, args, writes_cache,
-                             ctx.err, bias=self.qkv_bias_t, unit_norm_eps=self.unit_norm_eps, norm_dim=self.key_dim,
-                             has_kv=self.own_kv)
+                             ctx.err, bias=self.qkv_bias_t, unit_norm_eps=self.qk_norm_eps if norm_first else self.unit_norm_eps,
+                             norm_dim=self.key_dim, has_kv=self.own_kv, interleaved=self.interleaved, norm_first=norm_first,
+                             q_norm=self.q_norm, k_norm=self.k_norm)
+        blocks = None
+        if self.pool > 0:
+            blocks = ops.KvSiteArgs(site["blocks"].storage, site["blocks"].table, self.n_kv, self.head_dim)
+            ops.pool_cache_write(ctx.cu_q, ctx.tok_pos, ctx.slots, args, blocks, self.pool, ctx.max_q_len, ctx.err)
         attended = torch.empty_like(q)
-        fast = ctx.attention == "auto" and x.dtype == torch.bfloat16 and self.head_dim in ops.FAST_ATTENTION_HEAD_DIMS
+        fast = (ctx.attention == "auto" and x.dtype == torch.bfloat16 and self.head_dim in ops.FAST_ATTENTION_HEAD_DIMS
+                and self.pool == 0)
         if fast and ctx.is_decode and n == ctx.n_seqs:
             n_splits = self.decode_splits(ctx)
             ops.attention_decode(q, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs, self.scale,
@@ -211,7 +285,9 @@ class GqaAttention(Mixer):
         else:
             ops.attention_generic(q, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs, ctx.max_q_len,
                                   self.scale, self.window, ctx.err, scratch=ctx.decode_scratch, max_kv_len=ctx.max_kv_len,
-                                  sinks=self.sinks, chunk=self.chunk, softcap=self.softcap)
+                                  sinks=self.sinks, chunk=self.chunk, softcap=self.softcap, blocks=blocks, pool=self.pool)
+        if self.gated:
+            ops.head_gate(attended, gates, self.n_heads)
         return ops.linear(attended, self.o_weight, self.o_bias_t) if self.o_bias_t is not None else ops.linear_rows(attended, self.o_weight)
 
     # ---- the form for decode steps of up to 64 sequences that works on the residual stream in place: the norm, bias,

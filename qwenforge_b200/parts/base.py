@@ -44,7 +44,7 @@ class TensorSpec:
     """One tensor of the weight files.
 
     init  how the random-weights mode draws it: "matrix" N(0, 0.02), "bias" N(0, 0.02), "norm" 1 + N(0, 0.1),
-          "logit" N(0, 1)
+          "logit" N(0, 1), "conv" (1 + N(0, 0.5)) / sqrt(taps), "fraction" sigmoid(N(0, 1))
     keep  "compute": kept in the activation dtype (bfloat16, or float32 on the 32-bit path)
           "stored":  kept as the file stores it if that is a 32-bit float, else as "compute"
           "int32":   an integer table, kept as int32
@@ -93,7 +93,37 @@ class Part:
         return []
 
 
-class PendingNormed:
+class Pending:
+    """What a block may leave in the place of a plain pending output: something that still has to reach the residual
+    stream and knows how (`add_to`). A block that can fold it into its own first kernel names its class in
+    `accepts_pending`; for every other block, and at the end of the schedule, the model calls `add_to` itself."""
+
+    def add_to(self, hidden: torch.Tensor) -> None:
+        raise NotImplementedError
+
+    def value(self) -> torch.Tensor:
+        """The float32 tensor that will be added (for diagnosis; not on the product path)."""
+        raise NotImplementedError
+
+
+class PendingPair(Pending):
+    """The outputs of two sublayers that read the same input (a parallel layer): their sum goes into the stream, summed
+    with each other first. Either may be None."""
+    __slots__ = ("a", "b")
+
+    def __init__(self, a, b=None):
+        self.a, self.b = a, b
+
+    def add_to(self, hidden: torch.Tensor) -> None:
+        from .. import ops
+        ops.residual_add_pair(hidden, self.a, self.b)
+
+    def value(self) -> torch.Tensor:
+        parts = [t.to(torch.float32) for t in (self.a, self.b) if t is not None]
+        return parts[0] + parts[1] if len(parts) == 2 else parts[0]
+
+
+class PendingNormed(Pending):
     """A sublayer's output that still has to be normalised (RMS, weight, eps) and added to the residual stream: what a
     block with norms after its sublayers hands to whoever runs next, so that the addition rides on that part's first norm
     kernel (`ops.sandwich_norm`). The model resolves it itself before anything that only knows plain deltas."""

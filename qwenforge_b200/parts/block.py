@@ -7,7 +7,8 @@ from __future__ import annotations
 
 import torch
 
-from .base import Norm, Part, PendingNormed
+from ..cache import BundleNeed
+from .base import Norm, Part, PendingNormed, PendingPair
 from .registry import build_part, register_part
 
 
@@ -92,5 +93,52 @@ class SandwichBlock(Part):
         return PendingNormed(run(x, ctx), *self.feed_forward_post_norm.fused_rms())
 
 
+class ParallelBlock(Part):
+    """One norm that both sublayers read:  h = norm(x);  x += mixer(in(h)) + feed_forward(h).
+    Reads the layer spec's parts `norm`, `mixer` and, if the layer has them, `feed_forward` and `mixer_input` (a part of role
+    "mixer_input" that filters what the mixer reads and may keep a state of its own per sequence, such as a token shift;
+    the feed-forward reads h as it is). The two outputs stay pending as a pair: the next norm kernel of a block of this
+    kind adds their sum to the float32 stream on its way."""
+
+    accepts_pending = (PendingPair,)
+
+    def __init__(self, layer_spec):
+        self.kind = "parallel"
+        self.norm = build_part("norm", layer_spec.part("norm"))
+        self.mixer = build_part("mixer", layer_spec.part("mixer"))
+        self.mixer_input = build_part("mixer_input", layer_spec.part("mixer_input")) if "mixer_input" in layer_spec.parts else None
+        self.feed_forward = build_part("feed_forward", layer_spec.part("feed_forward")) if "feed_forward" in layer_spec.parts else None
+        self.pair_norm = bool(getattr(self.norm, "takes_pair", False))   # its kernel adds two pending outputs on its way
+
+    def sub_parts(self):
+        return [p for p in (self.norm, self.mixer_input, self.mixer, self.feed_forward) if p is not None]
+
+    def cache_need(self):
+        need = self.mixer.cache_need()
+        if self.mixer_input is None or self.mixer_input.cache_need() is None:
+            return need
+        return BundleNeed((("input", self.mixer_input.cache_need()), ("mixer", need)))
+
+    def forward(self, hidden, delta, ctx, site, writes_cache):
+        if isinstance(delta, PendingPair):
+            if self.pair_norm:
+                h = self.norm.forward(hidden, delta.a, delta.b)
+            else:
+                delta.add_to(hidden)
+                h = self.norm.forward(hidden, None)
+        else:
+            h = self.norm.forward(hidden, delta)
+        mixer_site, u = site, h
+        if self.mixer_input is not None:
+            bundled = self.mixer_input.cache_need() is not None
+            if bundled and not writes_cache:
+                raise ValueError("parallel: a layer whose mixer input keeps a state cannot read another entry's cache")
+            u = self.mixer_input.forward(h, ctx, site["input"] if bundled else None)
+            mixer_site = site["mixer"] if bundled else site
+        mixed = self.mixer.forward(u, ctx, mixer_site, writes_cache)
+        return PendingPair(mixed, self.feed_forward.forward(h, ctx) if self.feed_forward is not None else None)
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "parallel", ParallelBlock)
 register_part("block", "sandwich_norm", SandwichBlock)

@@ -8,6 +8,14 @@
   expert(v) = D_e (silu(G_e v) * (U_e v)),  no biases
 (computed as silu(w_e (G_e h)) * (w_e (U_e h)) for a weight on the input: the same numbers, the scale applied to float32 sums)
 
+Options, each a parameter of the spec:
+  router_bias  z = R h + r, a float32 bias per expert, added before the choice
+  gate         "clamped": expert(v) = D_e (g * sigmoid(alpha g) * (u + 1)) with g = min(G_e v, limit), u = clamp(U_e v, -limit, limit)
+               (`limit`, `alpha`) instead of the SwiGLU; the weight is then on the output
+  shared       one more expert of the same form with sizes of its own (`size`, `limit`) that every token gets, added to the
+               chosen experts' sum; with `gated` it is multiplied by sigmoid(s . h), one number per token
+(score "softmax" with `renormalize` is the softmax over the chosen logits alone.)
+
 Routing, sorting by expert and the experts' products all stay on the device (`ops.moe_plan`, `ops.expert_linear`: one
 launch per product for all experts, sized by what any routing can need), so the part is graph safe: a decode graph
 replays it with other routings every step.
@@ -39,7 +47,17 @@ class RoutedExperts(FeedForward):
             raise ValueError(f"routed_experts: score {self.score!r} / weight_on {self.weight_on!r} not understood")
         if not 1 <= self.top <= min(self.n_experts, 16):
             raise ValueError(f"routed_experts: top {self.top} of {self.n_experts} experts is not supported (1..16)")
-        self.router = self.gate_up = self.down = None
+        self.router_bias = bool(p.get("router_bias", False))
+        self.gate = str(p.get("gate", "swiglu"))
+        self.limit, self.alpha = float(p.get("limit") or 0.0), float(p.get("alpha") or 0.0)
+        if self.gate not in ("swiglu", "clamped") or (self.gate == "clamped" and (self.weight_on != "output" or self.limit <= 0)):
+            raise ValueError("routed_experts: gate is 'swiglu' or 'clamped'; the clamped gate takes a positive limit and the weight on the output")
+        self.shared = dict(p["shared"]) if p.get("shared") else None
+        self.router = self.gate_up = self.down = self.bias = None
+        self.shared_gate_up = self.shared_down = self.shared_logit = None
+        # what a block that sums rows inside its next norm kernel may call instead of `forward`: only where the chosen
+        # experts' rows are the whole output
+        self.forward_rows = self._routed_rows if self.shared is None else None
 
     def tensor_specs(self):
         specs = [TensorSpec(self.file_name("router"), (self.n_experts, self.hidden))]
@@ -47,6 +65,14 @@ class RoutedExperts(FeedForward):
             specs += [TensorSpec(self.file_name(f"gate.{e}"), (self.inter, self.hidden)),
                       TensorSpec(self.file_name(f"up.{e}"), (self.inter, self.hidden)),
                       TensorSpec(self.file_name(f"down.{e}"), (self.hidden, self.inter))]
+        if self.router_bias:
+            specs.append(TensorSpec(self.file_name("router_bias"), (self.n_experts,), init="logit", keep="float32"))
+        if self.shared is not None:
+            size = int(self.shared["size"])
+            specs += [TensorSpec(self.file_name("shared_gate"), (size, self.hidden)), TensorSpec(self.file_name("shared_up"), (size, self.hidden)),
+                      TensorSpec(self.file_name("shared_down"), (self.hidden, size))]
+            if self.shared.get("gated"):
+                specs.append(TensorSpec(self.file_name("shared_logit"), (1, self.hidden)))
         return specs
 
     def kernel_libraries(self, dtype):
@@ -57,28 +83,55 @@ class RoutedExperts(FeedForward):
         self.router = t("router")
         self.gate_up = torch.stack([torch.cat((t(f"gate.{e}"), t(f"up.{e}")), dim=0) for e in range(self.n_experts)]).contiguous()
         self.down = torch.stack([t(f"down.{e}") for e in range(self.n_experts)]).contiguous()
+        if self.router_bias:
+            self.bias = t("router_bias").to(torch.float32).contiguous()
+        if self.shared is not None:
+            self.shared_gate_up = torch.cat((t("shared_gate"), t("shared_up")), dim=0).contiguous()
+            self.shared_down = t("shared_down")
+            if self.shared.get("gated"):
+                self.shared_logit = t("shared_logit")
 
     def step_weights(self):
-        return [self.router, self.gate_up, self.down]
+        return [w for w in (self.router, self.gate_up, self.down, self.bias, self.shared_gate_up, self.shared_down, self.shared_logit)
+                if w is not None]
 
     def forward(self, x, ctx):
         out = torch.empty_like(x)
-        r = self.forward_rows(x, ctx)
-        ops.moe_combine(r.rows, self._plan, out, r.row_weight is not None)
+        r = self._routed_rows(x, ctx)
+        extra = logit = None
+        if self.shared is not None:   # the expert that every token gets rides on the kernel that sums the chosen ones
+            act = torch.empty((x.shape[0], int(self.shared["size"])), dtype=x.dtype, device=x.device)
+            if self.gate == "clamped":
+                ops.clamped_glu(ops.linear_rows(x, self.shared_gate_up), float(self.shared.get("limit") or self.limit), self.alpha, act)
+            else:
+                ops.swiglu(ops.linear_rows(x, self.shared_gate_up), act)
+            extra = ops.linear_rows(act, self.shared_down)
+            if self.shared_logit is not None:
+                logit = ops.linear_rows(x, self.shared_logit, out_dtype=torch.float32)
+        ops.moe_combine(r.rows, self._plan, out, r.row_weight is not None, extra, logit)
         return out
 
-    def forward_rows(self, x, ctx) -> RowSum:
-        """The experts' output rows, `top` per token and not yet summed (see `RowSum`)."""
+    def _routed_rows(self, x, ctx) -> RowSum:
+        """The chosen experts' output rows, `top` per token and not yet summed (see `RowSum`)."""
         # float32 logits from the rows as the experts see them (their bfloat16 rounding on the 16-bit path: products of
         # bfloat16 numbers are exact in float32, and the sums are float32)
         n = x.shape[0]
         tile_rows = ops.moe_tile_rows(n, self.n_experts, self.top, self.gate_up)
         soft, renorm = self.score == "softmax", self.renormalize
         if n * self.n_experts <= ops.MOE_FUSED_ROUTER_MAX:
-            plan = ops.moe_plan(None, self.top, soft, renorm, tile_rows, x=x, router=self.router)   # few tokens: one launch
+            plan = ops.moe_plan(None, self.top, soft, renorm, tile_rows, x=x, router=self.router, bias=self.bias)   # few tokens: one launch
         else:
-            plan = ops.moe_plan(ops.linear(x, self.router, out_dtype=torch.float32), self.top, soft, renorm, tile_rows)
+            plan = ops.moe_plan(ops.linear(x, self.router, out_dtype=torch.float32), self.top, soft, renorm, tile_rows, bias=self.bias)
         self._plan = plan
+        if self.gate == "clamped":
+            # the rows are read through the plan's row map; both halves in one product, then the clamped gate
+            gate_up = torch.empty((plan.pairs, 2 * self.inter), dtype=x.dtype, device=x.device)
+            ops.expert_linear(x, self.gate_up, plan, gate_up, gather=True)
+            act = torch.empty((plan.pairs, self.inter), dtype=x.dtype, device=x.device)
+            ops.clamped_glu(gate_up, self.limit, self.alpha, act)
+            rows = torch.empty((plan.pairs, self.hidden), dtype=x.dtype, device=x.device)
+            ops.expert_linear(act, self.down, plan, rows)
+            return RowSum(rows, plan.dest, self.top, plan.sorted_weight)
         # A weight on the expert's input moves behind its first product (G (w h) = w (G h), and the same for U), where it
         # meets float32 sums.
         on_input = self.weight_on == "input"

@@ -43,4 +43,39 @@ class RmsNorm(Norm):
         return [self.weight]
 
 
+class DynamicTanh(Norm):
+    """Dynamic Tanh in a norm's place: tanh(alpha * x) * w + b, element by element; no mean, no variance, no eps.
+    params: width. tensors: weight [width], bias [width], alpha [] (a scalar, read once when the weights are bound).
+    `forward` takes up to two pending outputs and adds their sum to the stream on its way (float32)."""
+    takes_pair = True
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.width = int(self.params["width"])
+        self.weight = self.bias = None
+        self.alpha = 1.0
+
+    def tensor_specs(self):
+        return [TensorSpec(self.file_name("weight"), (self.width,), init="norm"),
+                TensorSpec(self.file_name("bias"), (self.width,), init="bias"),
+                TensorSpec(self.file_name("alpha"), (), init="norm", keep="float32")]
+
+    def kernel_libraries(self, dtype):
+        return {"norm"}
+
+    def bind(self, tensors, dtype, device):
+        self.weight = tensors[self.file_name("weight")]
+        self.bias = tensors[self.file_name("bias")]
+        self.alpha = float(tensors[self.file_name("alpha")].float().item())
+
+    def forward(self, hidden: torch.Tensor, delta: Optional[torch.Tensor], second: Optional[torch.Tensor] = None) -> torch.Tensor:
+        out = torch.empty(hidden.shape, dtype=self.weight.dtype, device=hidden.device)
+        ops.add_dyt_norm(hidden, delta, second, self.weight, self.bias, self.alpha, out)
+        return out
+
+    def step_weights(self):
+        return [self.weight, self.bias]
+
+
 register_part("norm", "rms_norm", RmsNorm)
+register_part("norm", "dynamic_tanh", DynamicTanh)

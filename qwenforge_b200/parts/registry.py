@@ -4,7 +4,7 @@ from __future__ import annotations
 
 from ..config.spec import PartSpec
 
-_ROLES = ("norm", "mixer", "feed_forward", "position", "block", "embedding", "head")
+_ROLES = ("norm", "mixer", "feed_forward", "position", "block", "embedding", "head", "stream", "mixer_input")
 _REGISTRY: dict[str, dict[str, type]] = {role: {} for role in _ROLES}
 
 

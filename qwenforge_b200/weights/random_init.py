@@ -27,6 +27,10 @@ def draw_tensor(spec: TensorSpec, generator: torch.Generator, store_dtype: torch
         value = 0.02 * noise
     elif spec.init == "logit":
         value = noise
+    elif spec.init == "conv":        # taps of a short convolution: about equal weight, a sum of order one
+        value = (1.0 + 0.5 * noise) / spec.shape[-1] ** 0.5
+    elif spec.init == "fraction":    # a mixing weight between 0 and 1
+        value = torch.sigmoid(noise)
     else:
         raise ValueError(f"tensor {spec.name!r}: unknown init {spec.init!r}")
     return value if spec.keep == "stored" else value.to(store_dtype)
@@ -47,14 +51,19 @@ def random_state_on_device(specs, seed: int, dtype: torch.dtype, device) -> dict
         if spec.keep == "int32":
             out[name] = torch.zeros(spec.shape, dtype=torch.int32, device=device)
             continue
-        if spec.init not in ("norm", "matrix", "bias", "logit"):
+        if spec.init not in ("norm", "matrix", "bias", "logit", "conv", "fraction"):
             raise ValueError(f"tensor {spec.name!r}: unknown init {spec.init!r}")
         kept = torch.float32 if spec.keep in ("stored", "float32") else dtype
         value = torch.empty(spec.shape, dtype=kept, device=device)
         flat = value.view(-1)
         for begin in range(0, flat.numel(), 1 << 27):  # float32 draws of at most 512 MB at a time
             noise = torch.randn(min(1 << 27, flat.numel() - begin), generator=generator, dtype=torch.float32, device=device)
-            noise = 1.0 + 0.1 * noise if spec.init == "norm" else noise if spec.init == "logit" else 0.02 * noise
+            if spec.init == "conv":
+                noise = (1.0 + 0.5 * noise) / spec.shape[-1] ** 0.5
+            elif spec.init == "fraction":
+                noise = torch.sigmoid(noise)
+            else:
+                noise = 1.0 + 0.1 * noise if spec.init == "norm" else noise if spec.init == "logit" else 0.02 * noise
             flat[begin:begin + noise.numel()] = noise.to(kept)
         out[name] = value
     return out

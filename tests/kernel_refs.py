@@ -71,10 +71,10 @@ def _kv_rows(site, slot, positions, head, which):
 
 
 def rope_cache_write(qkv, tok_seq, tok_pos, slots, inv_freq, rot_dim, n_heads, q_out, site, write_cache, err, bias=None,
-                     unit_norm_eps=None, norm_dim=0, has_kv=True):
+                     unit_norm_eps=None, norm_dim=0, has_kv=True, interleaved=False, norm_first=False, q_norm=None, k_norm=None):
     n = qkv.shape[0]
     d, kvh = site.head_dim, site.kv_heads
-    x = _f(qkv)
+    x = _f(qkv)[:, :(n_heads + (2 * kvh if has_kv else 0)) * d]
     if bias is not None:
         x = x + _f(bias)
     q = x[:, :n_heads * d].reshape(n, n_heads, d).clone()
@@ -83,7 +83,19 @@ def rope_cache_write(qkv, tok_seq, tok_pos, slots, inv_freq, rot_dim, n_heads, q
         v = x[:, (n_heads + kvh) * d:].reshape(n, kvh, d)
     else:
         k, v = q[:, :0].clone(), None
-    if inv_freq is not None and rot_dim > 0:
+    if unit_norm_eps is not None and norm_first:
+        over = norm_dim or d
+        for t, w in ((q, q_norm), (k, k_norm)):
+            t[..., :over] = t[..., :over] / torch.sqrt(t[..., :over].square().mean(-1, keepdim=True) + unit_norm_eps) \
+                * (1.0 if w is None else _f(w))
+    if inv_freq is not None and rot_dim > 0 and interleaved:
+        angle = (tok_pos.to(torch.float32).unsqueeze(-1) * inv_freq.to(torch.float32)).to(torch.float64)
+        cos, sin = angle.cos().unsqueeze(1), angle.sin().unsqueeze(1)
+        for t in (q, k):
+            x1, x2 = t[..., 0:rot_dim:2].clone(), t[..., 1:rot_dim:2].clone()
+            t[..., 0:rot_dim:2] = x1 * cos - x2 * sin
+            t[..., 1:rot_dim:2] = x2 * cos + x1 * sin
+    elif inv_freq is not None and rot_dim > 0:
         angle = (tok_pos.to(torch.float32).unsqueeze(-1) * inv_freq.to(torch.float32)).to(torch.float64)
         cos, sin = angle.cos().unsqueeze(1), angle.sin().unsqueeze(1)
         half = rot_dim // 2
@@ -91,7 +103,7 @@ def rope_cache_write(qkv, tok_seq, tok_pos, slots, inv_freq, rot_dim, n_heads, q
             x1, x2 = t[..., :half].clone(), t[..., half:rot_dim].clone()
             t[..., :half] = x1 * cos - x2 * sin
             t[..., half:rot_dim] = x2 * cos + x1 * sin
-    if unit_norm_eps is not None:
+    if unit_norm_eps is not None and not norm_first:
         over = norm_dim or d
         for t in (q, k):
             t /= torch.sqrt(t[..., :over].square().mean(-1, keepdim=True) + unit_norm_eps)
@@ -128,7 +140,7 @@ def gather_keys(site, slot, lo, hi):
 
 
 def attention_generic(q, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q_len, scale, window, err, scratch=None, max_kv_len=None,
-                      sinks=None, shared_values=False, chunk=0, softcap=0.0):
+                      sinks=None, shared_values=False, chunk=0, softcap=0.0, blocks=None, pool=0):
     d, kvh = site.head_dim, site.kv_heads
     groups = n_heads // kvh
     for s in range(n_seqs):
@@ -146,6 +158,9 @@ def attention_generic(q, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q
                 k = v = gather_keys(site, slot, lo, p + 1)
             else:
                 k, v = gather_kv(site, slot, lo, p + 1)
+            if pool > 0 and p - window + 1 >= pool:   # the rows of the blocks that lie wholly before the window
+                bk, bv = gather_kv(blocks, slot, 0, (p - window + 1) // pool)
+                k, v = torch.cat((bk, k), dim=1), torch.cat((bv, v), dim=1)
             qt = _f(q[t]).view(n_heads, d)
             k = k.repeat_interleave(groups, dim=0)
             v = v.repeat_interleave(groups, dim=0)
@@ -255,10 +270,12 @@ def scaled_swiglu(gate_up, row_scale, out):
     out.copy_((g * torch.sigmoid(g) * u).to(out.dtype))
 
 
-def moe_plan(logits, top, softmax_scores=False, renormalize=False, tile_rows=64, x=None, router=None):
+def moe_plan(logits, top, softmax_scores=False, renormalize=False, tile_rows=64, x=None, router=None, bias=None):
     if logits is None:
         logits = (_f(x) @ _f(router).T)
     z = logits.to(torch.float32)
+    if bias is not None:
+        z = z + bias.to(torch.float32)
     scores = torch.softmax(z, -1) if softmax_scores else torch.sigmoid(z)
     chosen = torch.topk(scores, top, dim=-1)
     weights = chosen.values / chosen.values.sum(-1, keepdim=True) if renormalize else chosen.values
@@ -281,11 +298,14 @@ def moe_gather(x, plan, out, scale_input):
     out.copy_(rows.to(out.dtype))
 
 
-def moe_combine(y, plan, out, scale_output):
+def moe_combine(y, plan, out, scale_output, extra=None, extra_gate=None):
     rows = _f(y)
     if scale_output:
         rows = rows * _f(plan.sorted_weight)[:, None]
-    out.copy_(rows[plan.dest.long()].view(plan.n_tokens, plan.top, -1).sum(1).to(out.dtype))
+    total = rows[plan.dest.long()].view(plan.n_tokens, plan.top, -1).sum(1)
+    if extra is not None:
+        total = total + _f(extra) * (1.0 if extra_gate is None else torch.sigmoid(_f(extra_gate)).view(-1, 1))
+    out.copy_(total.to(out.dtype))
 
 
 def expert_linear(x, weight, plan, out, gather=False):
@@ -301,6 +321,8 @@ def bias_act(x, bias, kind, out):
         y = 0.5 * z * (1 + torch.tanh(0.7978845608028654 * (z + 0.044715 * z ** 3)))
     elif kind == "silu":
         y = z * torch.sigmoid(z)
+    elif kind == "gelu":
+        y = 0.5 * z * (1 + torch.erf(z / 2 ** 0.5))
     else:
         y = torch.relu(z)
     out.copy_(y.to(out.dtype))
@@ -379,7 +401,7 @@ def gated_group_norm(y, gate, weight, eps, out, n_parts, n_heads, gate_kind, gat
     out.copy_(z.to(out.dtype))
 
 
-def causal_conv_silu(x, weight, bias, cu_q, tok_seq, slots, state, offset, out):
+def causal_conv_silu(x, weight, bias, cu_q, tok_seq, slots, state, offset, out, activation="silu"):
     n, c = x.shape
     taps = weight.shape[1]
     for s in range(cu_q.numel() - 1):
@@ -392,12 +414,52 @@ def causal_conv_silu(x, weight, bias, cu_q, tok_seq, slots, state, offset, out):
         z = sum(padded[j:j + e - b] * _f(weight)[:, j] for j in range(taps))
         if bias is not None:
             z = z + _f(bias)
-        out[b:e] = (z * torch.sigmoid(z)).to(out.dtype)
-        if slot >= 0:
+        out[b:e] = (z * torch.sigmoid(z) if activation == "silu" else z).to(out.dtype)
+        if slot >= 0 and taps > 1:
             state[slot, offset:offset + (taps - 1) * c] = padded[padded.shape[0] - (taps - 1):].reshape(-1).float()
 
 
-ALL = dict(bias_act=bias_act, softcap_=softcap_, stabilized_gates=stabilized_gates, decay_gates=decay_gates,
+def causal_conv(x, weight, bias, cu_q, tok_seq, slots, state, offset, out):
+    causal_conv_silu(x, weight, bias, cu_q, tok_seq, slots, state, offset, out, activation="none")
+
+
+def add_dyt_norm(hidden, a, b, weight, bias, alpha, out):
+    if a is not None or b is not None:
+        hidden += ((0 if a is None else _f(a)) + (0 if b is None else _f(b))).to(hidden.dtype)
+    out.copy_((torch.tanh(alpha * _f(hidden)) * _f(weight) + _f(bias)).to(out.dtype))
+
+
+def residual_add_pair(hidden, a, b):
+    if a is not None or b is not None:
+        hidden += ((0 if a is None else _f(a)) + (0 if b is None else _f(b))).to(hidden.dtype)
+
+
+def stream_pair(hidden, a, b, other, out):
+    x = _f(hidden) + (0 if a is None else _f(a)) + (0 if b is None else _f(b))
+    out.copy_(torch.cat((x, _f(other)), dim=-1).to(out.dtype))
+
+
+def head_gate(x, gate, n_heads):
+    rows = x.shape[0]
+    x.copy_((_f(x).view(rows, n_heads, -1) * torch.sigmoid(_f(gate))[:, :, None]).view(rows, -1).to(x.dtype))
+
+
+def pool_cache_write(cu_q, tok_pos, slots, site, blocks, pool, max_q_len, err):
+    for s in range(slots.numel()):
+        slot, b, e = int(slots[s]), int(cu_q[s]), int(cu_q[s + 1])
+        if slot < 0 or e <= b:
+            continue
+        start = int(tok_pos[b])
+        for block in range(start // pool, (start + e - b) // pool):
+            k, v = gather_kv(site, slot, block * pool, block * pool + pool)      # [kvh, pool, d]
+            page = int(blocks.table[slot, block // PAGE])
+            assert page >= 0, "reference: write to a page of block rows that is not held"
+            blocks.storage[page, 0, :, block % PAGE, :] = k.mean(1).to(blocks.storage.dtype)
+            blocks.storage[page, 1, :, block % PAGE, :] = v.mean(1).to(blocks.storage.dtype)
+
+
+ALL = dict(causal_conv=causal_conv, add_dyt_norm=add_dyt_norm, residual_add_pair=residual_add_pair, stream_pair=stream_pair,
+           head_gate=head_gate, pool_cache_write=pool_cache_write, bias_act=bias_act, softcap_=softcap_, stabilized_gates=stabilized_gates, decay_gates=decay_gates,
            outer_state_scan=outer_state_scan, gated_group_norm=gated_group_norm, causal_conv_silu=causal_conv_silu,
            expert_gate_takes=expert_gate_takes, linear_rows=linear_rows, moe_tile_rows=moe_tile_rows, scaled_swiglu=scaled_swiglu, embed_positions=embed_positions, sandwich_norm=sandwich_norm, clamped_glu=clamped_glu, latent_norm_cache=latent_norm_cache,
            head_linear=head_linear, moe_plan=moe_plan, moe_gather=moe_gather, moe_combine=moe_combine, expert_linear=expert_linear,
