@@ -116,7 +116,8 @@ class RoutedExperts(FeedForward):
         # float32 logits from the rows as the experts see them (their bfloat16 rounding on the 16-bit path: products of
         # bfloat16 numbers are exact in float32, and the sums are float32)
         n = x.shape[0]
-        tile_rows = ops.moe_tile_rows(n, self.n_experts, self.top, self.gate_up)
+        # (the large tile only where both products' operands allow it)
+        tile_rows = min(ops.moe_tile_rows(n, self.n_experts, self.top, self.gate_up), ops.moe_tile_rows(n, self.n_experts, self.top, self.down))
         soft, renorm = self.score == "softmax", self.renormalize
         if n * self.n_experts <= ops.MOE_FUSED_ROUTER_MAX:
             plan = ops.moe_plan(None, self.top, soft, renorm, tile_rows, x=x, router=self.router, bias=self.bias)   # few tokens: one launch

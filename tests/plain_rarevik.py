@@ -117,17 +117,16 @@ def pooled_window_attention(weights, p, m, h, eps):
     pooled_v = v[:n_blocks * pool].view(n_blocks, pool, g, vdim).mean(dim=1)
     sink = weights[p + "sink"].to(F)
     out = torch.zeros((t, heads, vdim), dtype=F)
+    per = heads // g
     for i in range(t):
         first = max(0, i - size + 1)
         seen = max(0, (i - size + 1) // pool)          # blocks b with b * pool + pool - 1 <= i - size
-        for head in range(heads):
-            kv = head // (heads // g)
-            keys = torch.cat((pooled_k[:seen, kv], k[first:i + 1, kv]), dim=0)
-            values = torch.cat((pooled_v[:seen, kv], v[first:i + 1, kv]), dim=0)
-            s = (keys @ q[i, head]) * float(m["scale"])
-            top = torch.maximum(s.max(), sink[head])
-            e = torch.exp(s - top)
-            out[i, head] = (e[:, None] * values).sum(dim=0) / (e.sum() + torch.exp(sink[head] - top))
+        keys = torch.cat((pooled_k[:seen], k[first:i + 1]), dim=0).repeat_interleave(per, dim=1)      # [n, heads, dim]
+        values = torch.cat((pooled_v[:seen], v[first:i + 1]), dim=0).repeat_interleave(per, dim=1)
+        s = torch.einsum("nhd,hd->hn", keys, q[i]) * float(m["scale"])
+        top = torch.maximum(s.max(dim=1).values, sink)
+        e = torch.exp(s - top[:, None])
+        out[i] = torch.einsum("hn,nhd->hd", e, values) / (e.sum(dim=1) + torch.exp(sink - top))[:, None]
     return out.reshape(t, heads * vdim) @ weights[p + "o"].to(F).T
 
 
@@ -141,13 +140,11 @@ def gated_window_attention(weights, p, m, h):
     v = (h @ weights[p + "v"].to(F).T).view(t, g, vdim)
     gate = torch.sigmoid(h @ weights[p + "g"].to(F).T)     # [T, heads]
     out = torch.zeros((t, heads, vdim), dtype=F)
+    per = heads // g
     for i in range(t):
         first = max(0, i - size + 1)
-        for head in range(heads):
-            kv = head // (heads // g)
-            s = (k[first:i + 1, kv] @ q[i, head]) * float(m["scale"])
-            w = torch.softmax(s, dim=0)
-            out[i, head] = (w[:, None] * v[first:i + 1, kv]).sum(dim=0) * gate[i, head]
+        s = torch.einsum("nhd,hd->hn", k[first:i + 1].repeat_interleave(per, dim=1), q[i]) * float(m["scale"])
+        out[i] = torch.einsum("hn,nhd->hd", torch.softmax(s, dim=1), v[first:i + 1].repeat_interleave(per, dim=1)) * gate[i][:, None]
     return out.reshape(t, heads * vdim) @ weights[p + "o"].to(F).T
 
 
@@ -230,6 +227,18 @@ def forward(cfg, weights, tokens, streams=None, margins=None):
         if streams is not None:
             streams.append(x)
     return dyt(x, weights, "final.norm") @ table.T
+
+
+def forward_logits(cfg, weights, tokens):
+    return forward(cfg, weights, tokens)
+
+
+def greedy_generate(cfg, weights, prompt, n_new):
+    tokens, out = list(prompt), []
+    for _ in range(n_new):
+        out.append(int(forward(cfg, weights, tokens)[-1].argmax()))
+        tokens.append(out[-1])
+    return out
 
 
 # ------------------------------------------------------------------ random weights for the tests
