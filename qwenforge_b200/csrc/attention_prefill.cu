@@ -14,6 +14,10 @@
 // `sinks` (float32 per query head, or null): a logit that joins the softmax's denominator once, unscaled, with no key and
 // no value. `shared_values`: the values are the keys themselves (pages of one plane, as a latent attention keeps them):
 // a page is fetched once and read as both.
+// `pool` > 0 (with a window): beside the window's keys a query at p sees one key and value for every block of `pool`
+// positions that lies wholly before its window (blocks b with b * pool + pool - 1 <= p - window). Those rows live in a
+// second cache of the same head shape, one row per block (`blocks`); its pages are walked first, by the same loop and the
+// same buffers, masked by how many blocks each row sees, and share the softmax with the window's keys.
 #include "mma.cuh"
 
 #define PF_WARPS 4
@@ -26,13 +30,18 @@ __device__ __forceinline__ float fast_tanh(float x) {
     return y;
 }
 
-template <int D, int G>
+template <int D, int G, bool POOLED>
 __global__ void __launch_bounds__(PF_THREADS * G, (D <= 64 ? 4 : 2) / G)
 prefill_flash_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const int* __restrict__ cu_q,
                      const int* __restrict__ tok_pos, const int* __restrict__ slots, KvSite<bf16> site, int n_heads,
                      int n_seqs, int n_tiles, int wave, float scale_log2, int window, int* err,
-                     const float* __restrict__ sinks, int shared_values, int mask_block, float cap_in, float cap_out) {
+                     const float* __restrict__ sinks, int shared_values, int mask_block, float cap_in, float cap_out,
+                     KvSite<bf16> blocks, int pool) {
     grid_chain_entry();
+    auto seen_of = [&](int pos) -> int {   // blocks of `pool` positions wholly before the window of a query at `pos`
+        const int past = pos - window + 1;
+        return POOLED && pool > 0 && window > 0 && past >= pool ? past / pool : 0;
+    };
     // capped scores: s <- cap * tanh(s * scale / cap) in base-2 units, cap_in = scale / cap, cap_out = cap * log2(e); the
     // capped score then needs no further scale
     const float sl2 = cap_out > 0.f ? 1.f : scale_log2;
@@ -76,12 +85,17 @@ prefill_flash_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const i
     const int last_pos = pos0 + n_rows - 1;
     const int lo_min = lo_of(pos0);
     const int p_begin = lo_min / QF_PAGE, p_end = last_pos / QF_PAGE + 1;
+    // the walk: n_pool pages of block rows first (walk index v < n_pool is page v of `blocks`), then pages p_begin .. p_end - 1
+    // of the positions (walk index v is page p_begin + v - n_pool)
+    const int n_pool = POOLED ? (seen_of(last_pos) + QF_PAGE - 1) / QF_PAGE : 0;
+    const int v_end = n_pool + p_end - p_begin;
 
     // this thread's two rows
     const int r[2] = {16 * warp + (lane >> 2), 16 * warp + (lane >> 2) + 8};
     const bool row_ok[2] = {r[0] < n_rows, r[1] < n_rows};
     const int row_pos[2] = {pos0 + r[0], pos0 + r[1]};
     const int row_lo[2] = {lo_of(row_pos[0]), lo_of(row_pos[1])};
+    const int row_seen[2] = {seen_of(row_pos[0]), seen_of(row_pos[1])};
     // the warp's rows span positions [warp_first, warp_last]
     const int warp_first = pos0 + 16 * warp, warp_last = min(pos0 + 16 * warp + 15, last_pos);
     const int warp_lo = lo_of(warp_first);
@@ -106,15 +120,19 @@ prefill_flash_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const i
     float m_run[2] = {QF_NEG_BIG, QF_NEG_BIG}, l_run[2] = {0.f, 0.f};
 
     const int* table_row = site.table + (long long)slot * site.table_stride;
-    // the pages of one turn: page first + g goes to group g's buffer; every thread helps to fetch all of them
+    const int* blocks_row = n_pool > 0 ? blocks.table + (long long)slot * blocks.table_stride : nullptr;
+    // the pages of one turn: walk index first + g goes to group g's buffer; every thread helps to fetch all of them
     auto load_pages = [&](int first, int buf) {
         for (int gi = 0; gi < G; ++gi) {
-            if (first + gi >= p_end) break;
-            const int page = table_row[first + gi];
+            const int v = first + gi;
+            if (v >= v_end) break;
+            const bool rows = POOLED && v < n_pool;
+            const KvSite<bf16>& from = rows ? blocks : site;
+            const int page = rows ? blocks_row[v] : table_row[p_begin + v - n_pool];
             const bool held = page >= 0;
             if (!held && threadIdx.x == 0) atomicOr(err, QF_ERR_NO_PAGE);
-            const bf16* kp = site.base + (long long)(held ? page : 0) * site.page_elems + (long long)kvh * QF_PAGE * D;
-            const bf16* vp = kp + (long long)site.kv_heads * QF_PAGE * D;
+            const bf16* kp = from.base + (long long)(held ? page : 0) * from.page_elems + (long long)kvh * QF_PAGE * D;
+            const bf16* vp = kp + (long long)from.kv_heads * QF_PAGE * D;
             constexpr int CH = D / 8;
             for (int i = threadIdx.x; i < QF_PAGE * CH; i += PF_THREADS * G) {
                 const int rr = i / CH, c = (i % CH) * 8;
@@ -124,19 +142,21 @@ prefill_flash_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const i
         }
     };
 
-    load_pages(p_begin, 0);
+    load_pages(0, 0);
     cp_async_commit();
-    for (int first = p_begin, turn = 0; first < p_end; first += G, ++turn) {
+    for (int first = 0, turn = 0; first < v_end; first += G, ++turn) {
         const int buf = turn & 1;
-        if (first + G < p_end) load_pages(first + G, buf ^ 1);
+        if (first + G < v_end) load_pages(first + G, buf ^ 1);
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
-        const int p = first + group;
+        const int v = first + group;
+        const bool rows = POOLED && v < n_pool;   // a page of block rows: its "positions" are block indices, seen from 0 up to a count
         const bf16* kb = k_s + ((size_t)buf * G + group) * QF_PAGE * LD;
         const bf16* vb = v_s + ((size_t)buf * G + group) * QF_PAGE * LD;
-        const int key0 = p * QF_PAGE;
-        if (p < p_end && warp_active && key0 <= warp_last && key0 + QF_PAGE > warp_lo) {
+        const int key0 = (rows ? v : p_begin + v - n_pool) * QF_PAGE;
+        const int span_last = rows ? seen_of(warp_last) - 1 : warp_last, span_lo = rows ? 0 : warp_lo;
+        if (v < v_end && warp_active && key0 <= span_last && key0 + QF_PAGE > span_lo) {
             float s[8][4];
 #pragma unroll
             for (int t = 0; t < 8; ++t) s[t][0] = s[t][1] = s[t][2] = s[t][3] = 0.f;
@@ -157,7 +177,8 @@ prefill_flash_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const i
 #pragma unroll
                     for (int e = 0; e < 4; ++e) s[t][e] = cap_out * fast_tanh(s[t][e] * cap_in);
             }
-            const bool full = key0 + QF_PAGE - 1 <= warp_first && key0 >= lo_of(warp_last);
+            const bool full = rows ? key0 + QF_PAGE <= seen_of(warp_first)
+                                   : key0 + QF_PAGE - 1 <= warp_first && key0 >= lo_of(warp_last);
             float corr[2], sum[2] = {0.f, 0.f};
             if (full) {
                 // the common case (every page left of the diagonal): no comparisons, one fused multiply-add and one
@@ -195,8 +216,8 @@ prefill_flash_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const i
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const int kj = key0 + 8 * t + 2 * (lane & 3) + e;
-                        const bool ok0 = kj <= row_pos[0] && kj >= row_lo[0];
-                        const bool ok1 = kj <= row_pos[1] && kj >= row_lo[1];
+                        const bool ok0 = rows ? kj < row_seen[0] : kj <= row_pos[0] && kj >= row_lo[0];
+                        const bool ok1 = rows ? kj < row_seen[1] : kj <= row_pos[1] && kj >= row_lo[1];
                         s[t][e] = ok0 ? s[t][e] * sl2 : QF_NEG_BIG;
                         s[t][2 + e] = ok1 ? s[t][2 + e] * sl2 : QF_NEG_BIG;
                         mx[0] = fmaxf(mx[0], s[t][e]);
@@ -306,30 +327,32 @@ prefill_flash_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const i
     }
 }
 
-template <int D, int G>
+template <int D, int G, bool POOLED>
 static int launch_groups(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots, KvSite<bf16> site,
                          int n_heads, int n_seqs, int max_q_len, float scale, int window, int* err, const float* sinks,
-                         int shared_values, int mask_block, float softcap, cudaStream_t stream) {
+                         int shared_values, int mask_block, float softcap, KvSite<bf16> block_rows, int pool, cudaStream_t stream) {
     size_t smem = (size_t)4 * G * QF_PAGE * (D + 8) * sizeof(bf16);
     const size_t merge = (size_t)(G - 1) * PF_WARPS * (D / 8 * 4 + 4) * 32 * sizeof(float);
     if (smem < merge) smem = merge;
-    cudaError_t e = cudaFuncSetAttribute(prefill_flash_kernel<D, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(prefill_flash_kernel<D, G, POOLED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     const int n_tiles = (max_q_len + PF_BM - 1) / PF_BM;
     const long long blocks = (long long)n_tiles * n_heads * n_seqs;
     if (blocks > 0x7fffffffll) return (int)cudaErrorInvalidValue;
-    return (int)launch_pdl(prefill_flash_kernel<D, G>, dim3((unsigned)blocks), dim3(PF_THREADS * G), smem, stream, (const bf16*)q,
+    return (int)launch_pdl(prefill_flash_kernel<D, G, POOLED>, dim3((unsigned)blocks), dim3(PF_THREADS * G), smem, stream, (const bf16*)q,
                            (bf16*)out, cu_q, tok_pos, slots, site, n_heads, n_seqs, n_tiles, qf_sm_count(),
                            scale * 1.4426950408889634f, window, err, sinks, shared_values, mask_block,
-                           softcap > 0.f ? scale / softcap : 0.f, softcap > 0.f ? softcap * 1.4426950408889634f : 0.f);
+                           softcap > 0.f ? scale / softcap : 0.f, softcap > 0.f ? softcap * 1.4426950408889634f : 0.f, block_rows, pool);
 }
 
 template <int D>
 static int launch(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots, void* base,
                   const int* table, long long page_elems, int table_stride, int kv_heads, int n_heads, int n_seqs,
                   int n_tokens, int max_q_len, int max_kv_len, float scale, int window, int* err, const float* sinks,
-                  int shared_values, int mask_block, float softcap, cudaStream_t stream) {
+                  int shared_values, int mask_block, float softcap, void* blocks_base, const int* blocks_table,
+                  long long blocks_page_elems, int blocks_table_stride, int pool, cudaStream_t stream) {
     KvSite<bf16> site{(bf16*)base, table, page_elems, table_stride, kv_heads, D};
+    KvSite<bf16> blocks{(bf16*)blocks_base, blocks_table, blocks_page_elems, blocks_table_stride, kv_heads, D};
     // Two groups of warps per tile when tiles walk many pages and all tiles find room on the SMs at once (a short
     // continuation over a long cache, one prompt of a few thousand tokens): what bounds the kernel then is the longest
     // tile's chain of pages, which two groups halve. With more tiles than room, the SMs are busy anyway and one group
@@ -339,9 +362,13 @@ static int launch(const void* q, void* out, const int* cu_q, const int* tok_pos,
     const long long tiles = (long long)min((max_q_len + PF_BM - 1) / PF_BM * n_seqs, n_tokens / PF_BM + n_seqs) * n_heads;
     int span = window > 0 && window + PF_BM < max_kv_len ? window + PF_BM : max_kv_len;
     if (mask_block > 0 && mask_block < span) span = mask_block;   // no tile walks more than its rows' block of the mask
+    if (pool > 0) span += max_kv_len / pool;                      // the rows of the blocks before the window
     const bool split = span >= 8 * QF_PAGE && tiles < (long long)qf_sm_count() * (D <= 64 ? 4 : 2);
-    return split ? launch_groups<D, 2>(q, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q_len, scale, window, err, sinks, shared_values, mask_block, softcap, stream)
-                 : launch_groups<D, 1>(q, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q_len, scale, window, err, sinks, shared_values, mask_block, softcap, stream);
+#define QF_GROUPS_ARGS q, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q_len, scale, window, err, sinks, shared_values, mask_block, \
+                       softcap, blocks, pool, stream
+    if (pool > 0) return split ? launch_groups<D, 2, true>(QF_GROUPS_ARGS) : launch_groups<D, 1, true>(QF_GROUPS_ARGS);
+    return split ? launch_groups<D, 2, false>(QF_GROUPS_ARGS) : launch_groups<D, 1, false>(QF_GROUPS_ARGS);
+#undef QF_GROUPS_ARGS
 }
 
 // The arguments of the generic attention kernel, `n_tokens` (the rows of q: all sequences' new tokens) and `max_kv_len`,
@@ -350,17 +377,22 @@ static int launch(const void* q, void* out, const int* cu_q, const int* tok_pos,
 // instantiation (the caller then uses the generic kernel).
 // mask_block > 0: a query sees only the keys of its own block of that many positions; softcap > 0: a score s (after the
 // scale) becomes softcap * tanh(s / softcap), with the hardware's approximate tanh.
-QF_EXPORT int qf_attention_prefill_masked(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots,
+// pool > 0: the rows of whole blocks of `pool` positions, kept in a second cache of the same head shape (blocks_*), join
+// the window's keys (see the top of the file).
+QF_EXPORT int qf_attention_prefill_pooled(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots,
                                           void* base, const int* table, long long page_elems, int table_stride, int kv_heads,
                                           int head_dim, int n_heads, int n_seqs, int n_tokens, int max_q_len, int max_kv_len,
                                           float scale, int window, int* err, const float* sinks, int shared_values,
-                                          int mask_block, float softcap, cudaStream_t stream) {
+                                          int mask_block, float softcap, void* blocks_base, const int* blocks_table,
+                                          long long blocks_page_elems, int blocks_table_stride, int pool, cudaStream_t stream) {
     if (n_seqs <= 0 || max_q_len <= 0) return 0;
     if (kv_heads <= 0 || n_heads % kv_heads) return (int)cudaErrorInvalidValue;
+    if (pool > 0 && (!blocks_base || !blocks_table || window <= 0 || shared_values)) return (int)cudaErrorInvalidValue;
 #define QF_CASE(DIM)                                                                                                 \
     case DIM:                                                                                                        \
         return launch<DIM>(q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads, n_heads,  \
-                           n_seqs, n_tokens, max_q_len, max_kv_len, scale, window, err, sinks, shared_values, mask_block, softcap, stream);
+                           n_seqs, n_tokens, max_q_len, max_kv_len, scale, window, err, sinks, shared_values, mask_block, softcap, \
+                           blocks_base, blocks_table, blocks_page_elems, blocks_table_stride, pool, stream);
     switch (head_dim) {
         QF_CASE(32)
         QF_CASE(64)
@@ -370,6 +402,16 @@ QF_EXPORT int qf_attention_prefill_masked(const void* q, void* out, const int* c
             return (int)cudaErrorInvalidValue;
     }
 #undef QF_CASE
+}
+
+QF_EXPORT int qf_attention_prefill_masked(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots,
+                                          void* base, const int* table, long long page_elems, int table_stride, int kv_heads,
+                                          int head_dim, int n_heads, int n_seqs, int n_tokens, int max_q_len, int max_kv_len,
+                                          float scale, int window, int* err, const float* sinks, int shared_values,
+                                          int mask_block, float softcap, cudaStream_t stream) {
+    return qf_attention_prefill_pooled(q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads, head_dim,
+                                       n_heads, n_seqs, n_tokens, max_q_len, max_kv_len, scale, window, err, sinks, shared_values,
+                                       mask_block, softcap, nullptr, nullptr, 0, 0, 0, stream);
 }
 
 QF_EXPORT int qf_attention_prefill_ex(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots,

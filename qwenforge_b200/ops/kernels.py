@@ -322,9 +322,10 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, to
                       slots: torch.Tensor, site: KvSiteArgs, n_heads: int, n_seqs: int, max_q_len: int, scale: float,
                       window: int, err: torch.Tensor, max_kv_len: Optional[int] = None,
                       sinks: Optional[torch.Tensor] = None, shared_values: bool = False, chunk: int = 0,
-                      softcap: float = 0.0) -> None:
+                      softcap: float = 0.0, blocks: Optional[KvSiteArgs] = None, pool: int = 0) -> None:
     """Tensor-core flash attention of spans of new tokens over the cache: bfloat16, head sizes 32/64/96/128.
-    `sinks`, `shared_values`, `chunk`, `softcap`: as in `attention_generic` (the cap with the hardware's approximate tanh).
+    `sinks`, `shared_values`, `chunk`, `softcap`, `blocks` and `pool`: as in `attention_generic` (the cap with the hardware's
+    approximate tanh).
     `max_kv_len`: an upper bound of any sequence's length after the step (None: unknown, taken as long); it only
     steers whether a tile of rows shares its pages among two groups of warps."""
     _dev("q", q, torch.bfloat16)
@@ -340,11 +341,17 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, to
         _dev("sinks", sinks, torch.float32)
         if sinks.numel() != n_heads:
             raise KernelError("attention_prefill: sinks must hold one float32 per query head")
-    _check(library("attention_prefill").qf_attention_prefill_masked(
+    if pool > 0:
+        if blocks is None or window <= 0 or shared_values or (blocks.kv_heads, blocks.head_dim) != (site.kv_heads, d):
+            raise KernelError("attention_prefill: rows of whole blocks need a window and a second cache of the same head shape")
+        _dev("block rows", blocks.storage, torch.bfloat16)
+    _check(library("attention_prefill").qf_attention_prefill_pooled(
         _ptr(q), _ptr(out), _ptr(cu_q), _ptr(tok_pos), _ptr(slots), _ptr(site.storage), _ptr(site.table),
         _LL(site.page_elems), _I(site.table_stride), _I(site.kv_heads), _I(d), _I(n_heads), _I(n_seqs), _I(q.shape[0]),
         _I(max_q_len), _I(1 << 30 if max_kv_len is None else int(max_kv_len)), _F(scale), _I(window), _ptr(err),
-        _ptr(sinks), _I(int(bool(shared_values))), _I(int(chunk)), _F(softcap), _stream()), "attention_prefill")
+        _ptr(sinks), _I(int(bool(shared_values))), _I(int(chunk)), _F(softcap), _ptr(blocks.storage if pool > 0 else None),
+        _ptr(blocks.table if pool > 0 else None), _LL(blocks.page_elems if pool > 0 else 0),
+        _I(blocks.table_stride if pool > 0 else 0), _I(int(pool)), _stream()), "attention_prefill")
 
 
 TC_ATTENTION_HEAD_DIMS = (64, 128)

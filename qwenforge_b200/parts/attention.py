@@ -271,9 +271,10 @@ class GqaAttention(Mixer):
             blocks = ops.KvSiteArgs(site["blocks"].storage, site["blocks"].table, self.n_kv, self.head_dim)
             ops.pool_cache_write(ctx.cu_q, ctx.tok_pos, ctx.slots, args, blocks, self.pool, ctx.max_q_len, ctx.err)
         attended = torch.empty_like(q)
-        fast = (ctx.attention == "auto" and x.dtype == torch.bfloat16 and self.head_dim in ops.FAST_ATTENTION_HEAD_DIMS
-                and self.pool == 0)
-        if fast and ctx.is_decode and n == ctx.n_seqs:
+        fast = ctx.attention == "auto" and x.dtype == torch.bfloat16 and self.head_dim in ops.FAST_ATTENTION_HEAD_DIMS
+        # (pooled rows: single tokens run on the kernel of portions too. What a token reads there is bounded by its window
+        # and a row per block before it, a few pages that need no cut into runs; the split-K kernel does not take the rows.)
+        if fast and ctx.is_decode and n == ctx.n_seqs and self.pool == 0:
             n_splits = self.decode_splits(ctx)
             ops.attention_decode(q, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs, self.scale,
                                  self.window, n_splits, ctx.decode_scratch, ctx.err, self.decode_plan(ctx), sinks=self.sinks,
@@ -281,7 +282,7 @@ class GqaAttention(Mixer):
         elif fast:
             ops.attention_prefill(q, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs, ctx.max_q_len,
                                   self.scale, self.window, ctx.err, max_kv_len=ctx.max_kv_len, sinks=self.sinks,
-                                  chunk=self.chunk, softcap=self.softcap)
+                                  chunk=self.chunk, softcap=self.softcap, blocks=blocks, pool=self.pool)
         else:
             ops.attention_generic(q, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs, ctx.max_q_len,
                                   self.scale, self.window, ctx.err, scratch=ctx.decode_scratch, max_kv_len=ctx.max_kv_len,

@@ -138,7 +138,7 @@ def two_caches(kv_heads, dim, dtype, pool=0, window=0):
     need = KvNeed(kv_heads, dim, window, pool=pool)
     if pool:
         need = BundleNeed((("kv", need), ("blocks", KvNeed(kv_heads, dim, every=pool))))
-    return [SequenceCache([need], 1024, 3, 1024, dtype, DEV) for _ in range(2)]
+    return [SequenceCache([need], 2048, 3, 1024, dtype, DEV) for _ in range(2)]
 
 
 @pytest.mark.parametrize("dtype", BOTH)
@@ -221,6 +221,40 @@ def test_rows_of_whole_blocks_join_the_window_under_a_learned_sink(dtype, heads,
         close(caches[0].site(0)["blocks"].storage, caches[1].site(0)["blocks"].storage, dtype, "rows of blocks", bf16=1e-2)
         close(outs[0], outs[1], dtype, f"attention {spans}", f32=1e-4, bf16=2e-2)
     assert float(caches[0].site(0)["blocks"].storage.abs().max()) > 0
+
+
+@pytest.mark.parametrize("heads,kv_heads,dim,window,pool", [(4, 1, 64, 128, 32), (6, 3, 96, 190, 7), (2, 2, 32, 1, 1), (6, 2, 128, 40, 16),
+                                                            (4, 2, 64, 9, 70)])
+def test_tensor_core_attention_takes_the_rows_of_whole_blocks(heads, kv_heads, dim, window, pool):
+    """The mma.sync kernel of prompts, portions and single tokens against the float32 SIMT kernel on the same pages: rows of
+    blocks that fill more than a page, tiles whose rows see different numbers of blocks, a learned sink."""
+    from qwenforge_b200 import ops
+    g = torch.Generator().manual_seed(pool)
+    dtype = torch.bfloat16
+    cache = two_caches(kv_heads, dim, dtype, pool=pool, window=window)[0]
+    sinks = rand(g, heads)
+    slots = [cache.open() for _ in range(3)]
+    for spans in ([(0, 700), (0, 3), (0, 130)], [(700, 1), (3, 1), (130, 1)], [(701, 69), (4, 200), (131, 2)], [(770, 1), (204, 1), (133, 1)]):
+        batch = Batch(slots, spans)
+        k = rand(g, batch.n_tokens, 2, kv_heads, dim, dtype=dtype)
+        q = rand(g, batch.n_tokens, heads * dim, dtype=dtype, spread=2.0)
+        cache.reserve([(slot, start + n) for slot, (start, n) in zip(slots, spans)])
+        cache.flush()
+        kv, rows = cache.site(0)["kv"], cache.site(0)["blocks"]
+        pages = kv.table[batch.slots.long()[batch.tok_seq.long()], (batch.tok_pos // 64).long()].long()
+        kv.storage[pages, :, :, (batch.tok_pos % 64).long(), :] = k
+        err = torch.zeros(1, dtype=torch.int32, device=DEV)
+        a, b = ops.KvSiteArgs(kv.storage, kv.table, kv_heads, dim), ops.KvSiteArgs(rows.storage, rows.table, kv_heads, dim)
+        ops.pool_cache_write(batch.cu_q, batch.tok_pos, batch.slots, a, b, pool, batch.max_q_len, err)
+        out, want = (torch.empty(batch.n_tokens, heads * dim, dtype=dtype, device=DEV) for _ in range(2))
+        ops.attention_prefill(q, out, batch.cu_q, batch.tok_pos, batch.slots, a, heads, 3, batch.max_q_len, dim ** -0.5, window, err,
+                              max_kv_len=batch.max_kv_len, sinks=sinks, blocks=b, pool=pool)
+        ops.attention_generic(q, want, batch.cu_q, batch.tok_pos, batch.slots, a, heads, 3, batch.max_q_len, dim ** -0.5, window, err,
+                              sinks=sinks, blocks=b, pool=pool)
+        assert int(err) == 0
+        close(out, want, dtype, f"{spans}", bf16=2e-2)
+        for slot, (start, n) in zip(slots, spans):
+            cache.advance(slot, n)
 
 
 @pytest.mark.parametrize("dtype", BOTH)
