@@ -250,12 +250,22 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ dest, const float* __restrict__ sorted_weight,
                    T* __restrict__ out, int n_tokens, int top, int width, int scale_output, const T* __restrict__ extra,
-                   const float* __restrict__ extra_gate) {
+                   const float* __restrict__ extra_gate, const T* __restrict__ gate_input, const T* __restrict__ gate_weight,
+                   int gate_k) {
     grid_chain_entry();
+    __shared__ float scratch[33];
     const int t = blockIdx.x;
     if (t >= n_tokens) return;
-    // an output that every token gets beside its chosen ones (`extra`), under a sigmoid gate of one logit per token
-    const float share = extra ? (extra_gate ? 1.f / (1.f + expf(-extra_gate[t])) : 1.f) : 0.f;
+    // an output that every token gets beside its chosen ones (`extra`), under a sigmoid gate of one logit per token: given,
+    // or formed here as the token's row times the gate's weights (float32 sums in a fixed order)
+    float share = extra ? 1.f : 0.f;
+    if (extra && extra_gate) share = 1.f / (1.f + expf(-extra_gate[t]));
+    if (extra && gate_weight) {
+        float sum = 0.f;
+        for (int c = threadIdx.x; c < gate_k; c += blockDim.x)
+            sum = fmaf(Num<T>::to_f(gate_input[(size_t)t * gate_k + c]), Num<T>::to_f(gate_weight[c]), sum);
+        share = 1.f / (1.f + expf(-block_sum(sum, scratch)));
+    }
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
         float sum = 0.f;
         for (int k = 0; k < top; ++k) {
@@ -307,21 +317,25 @@ QF_EXPORT int qf_moe_gather(int is_bf16, const void* x, const int* sorted_token,
 }
 
 // extra: [n_tokens][width] added to every token's sum (or null), times sigmoid(extra_gate[t]) where extra_gate (float32
-// [n_tokens]) is given.
+// [n_tokens]) is given, or times sigmoid(gate_input[t] . gate_weight) where gate_weight [gate_k] and gate_input
+// [n_tokens][gate_k] are.
 QF_EXPORT int qf_moe_combine_shared(int is_bf16, const void* y, const int* dest, const float* sorted_weight, void* out, int n_tokens,
                                     int top, int width, int scale_output, const void* extra, const float* extra_gate,
-                                    cudaStream_t stream) {
+                                    const void* gate_input, const void* gate_weight, int gate_k, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (is_bf16)
         return (int)launch_pdl(moe_combine_kernel<bf16>, dim3(n_tokens), dim3(128), 0, stream, (const bf16*)y, dest, sorted_weight,
-                               (bf16*)out, n_tokens, top, width, scale_output, (const bf16*)extra, extra_gate);
+                               (bf16*)out, n_tokens, top, width, scale_output, (const bf16*)extra, extra_gate,
+                               (const bf16*)gate_input, (const bf16*)gate_weight, gate_k);
     return (int)launch_pdl(moe_combine_kernel<float>, dim3(n_tokens), dim3(128), 0, stream, (const float*)y, dest, sorted_weight,
-                           (float*)out, n_tokens, top, width, scale_output, (const float*)extra, extra_gate);
+                           (float*)out, n_tokens, top, width, scale_output, (const float*)extra, extra_gate,
+                           (const float*)gate_input, (const float*)gate_weight, gate_k);
 }
 
 QF_EXPORT int qf_moe_combine(int is_bf16, const void* y, const int* dest, const float* sorted_weight, void* out, int n_tokens,
                              int top, int width, int scale_output, cudaStream_t stream) {
-    return qf_moe_combine_shared(is_bf16, y, dest, sorted_weight, out, n_tokens, top, width, scale_output, nullptr, nullptr, stream);
+    return qf_moe_combine_shared(is_bf16, y, dest, sorted_weight, out, n_tokens, top, width, scale_output, nullptr, nullptr, nullptr,
+                                 nullptr, 0, stream);
 }
 
 // The plan of a long step by three launches (see moe_route_kernel). expert_rows: int32 [n_experts], zero before the call.

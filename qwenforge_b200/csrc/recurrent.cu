@@ -407,20 +407,22 @@ QF_EXPORT int qf_gated_group_norm(int is_bf16, const float* y, const void* gate,
 // Causal convolution per channel over a sequence's tokens, then silu. A thread takes one (token, channel); what lies
 // before the step's first token comes from the sequence's state (its last taps - 1 inputs). A second kernel then moves
 // the step's last taps - 1 inputs into the state, a thread per (sequence, channel), reading all it needs before it writes.
+// In a step of ONE token per sequence (`single`) a channel's kept inputs have one reader, the thread of that token and
+// channel, which then moves them itself: no second kernel.
 #define CONV_MAX_TAPS 16
 
 template <typename T>
 __global__ void causal_conv_silu_kernel(const T* __restrict__ x, int x_stride, const float* __restrict__ weight,
                                         const float* __restrict__ bias, const int* __restrict__ cu_q,
                                         const int* __restrict__ tok_seq, const int* __restrict__ slots,
-                                        const float* __restrict__ state, long long slot_stride, long long offset, int taps,
-                                        int n_tokens, int channels, T* __restrict__ out, int plain) {
+                                        float* __restrict__ state, long long slot_stride, long long offset, int taps,
+                                        int n_tokens, int channels, T* __restrict__ out, int plain, int single) {
     grid_chain_entry();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (long long)n_tokens * channels) return;
     const int t = (int)(i / channels), c = (int)(i % channels);
     const int seq = tok_seq[t], at = t - cu_q[seq], slot = slots[seq];
-    const float* before = slot >= 0 ? state + slot * slot_stride + offset : nullptr;   // [taps - 1][channels]
+    float* before = slot >= 0 ? state + slot * slot_stride + offset : nullptr;   // [taps - 1][channels]
     float z = bias ? bias[c] : 0.f;
     for (int j = 0; j < taps; ++j) {          // oldest input first: the same order for every cut
         const int back = taps - 1 - j;
@@ -428,7 +430,10 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ x, int x_stride, c
         if (at - back >= 0) u = Num<T>::to_f(x[(size_t)(t - back) * x_stride + c]);
         else if (before) u = before[(size_t)(taps - 1 + at - back) * channels + c];
         z = fmaf(weight[(size_t)c * taps + j], u, z);
+        // the input that was `back` tokens back is `back + 1` back for the next token: one row further down
+        if (single && before && back >= 1 && back < taps - 1) before[(size_t)(taps - 2 - back) * channels + c] = u;
     }
+    if (single && before && taps > 1) before[(size_t)(taps - 2) * channels + c] = Num<T>::to_f(x[(size_t)t * x_stride + c]);
     out[(size_t)t * channels + c] = Num<T>::from_f(plain ? z : z / (1.f + expf(-z)));
 }
 
@@ -454,12 +459,12 @@ __global__ void conv_state_kernel(const T* __restrict__ x, int x_stride, const i
 template <typename T>
 static int launch_conv(const void* x, int x_stride, const float* weight, const float* bias, const int* cu_q, const int* tok_seq,
                        const int* slots, int n_seqs, float* state, long long slot_stride, long long offset, int taps,
-                       int n_tokens, int channels, void* out, int plain, cudaStream_t stream) {
+                       int n_tokens, int channels, void* out, int plain, int single, cudaStream_t stream) {
     const long long total = (long long)n_tokens * channels;
     cudaError_t e = launch_pdl(causal_conv_silu_kernel<T>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream,
-                               (const T*)x, x_stride, weight, bias, cu_q, tok_seq, slots, (const float*)state, slot_stride, offset,
-                               taps, n_tokens, channels, (T*)out, plain);
-    if (e != cudaSuccess || taps <= 1) return (int)e;
+                               (const T*)x, x_stride, weight, bias, cu_q, tok_seq, slots, state, slot_stride, offset,
+                               taps, n_tokens, channels, (T*)out, plain, single);
+    if (e != cudaSuccess || taps <= 1 || single) return (int)e;
     const long long pairs = (long long)n_seqs * channels;
     // launched the ordinary way: it must not start before every block of the convolution has read the old state
     conv_state_kernel<T><<<dim3((unsigned)((pairs + 255) / 256)), dim3(256), 0, stream>>>((const T*)x, x_stride, cu_q, slots, n_seqs,
@@ -467,17 +472,19 @@ static int launch_conv(const void* x, int x_stride, const float* weight, const f
     return (int)cudaGetLastError();
 }
 
-// plain: 1 leaves the activation out (the convolution alone).
+// plain: 1 leaves the activation out (the convolution alone). single: 1 promises that every sequence of the step brings
+// exactly one token (n_tokens == n_seqs).
 QF_EXPORT int qf_causal_conv(int is_bf16, const void* x, int x_stride, const float* weight, const float* bias,
                              const int* cu_q, const int* tok_seq, const int* slots, int n_seqs, float* state,
                              long long slot_stride, long long offset, int taps, int n_tokens, int channels, void* out, int plain,
-                             cudaStream_t stream) {
+                             int single, cudaStream_t stream) {
+    if (single && n_tokens != n_seqs) return (int)cudaErrorInvalidValue;
     if (n_tokens <= 0 || channels <= 0) return 0;
     if (taps < 1 || taps > CONV_MAX_TAPS) return (int)cudaErrorInvalidValue;
     return is_bf16 ? launch_conv<bf16>(x, x_stride, weight, bias, cu_q, tok_seq, slots, n_seqs, state, slot_stride, offset, taps,
-                                       n_tokens, channels, out, plain, stream)
+                                       n_tokens, channels, out, plain, single, stream)
                    : launch_conv<float>(x, x_stride, weight, bias, cu_q, tok_seq, slots, n_seqs, state, slot_stride, offset, taps,
-                                        n_tokens, channels, out, plain, stream);
+                                        n_tokens, channels, out, plain, single, stream);
 }
 
 QF_EXPORT int qf_causal_conv_silu(int is_bf16, const void* x, int x_stride, const float* weight, const float* bias,
@@ -485,5 +492,5 @@ QF_EXPORT int qf_causal_conv_silu(int is_bf16, const void* x, int x_stride, cons
                                   long long slot_stride, long long offset, int taps, int n_tokens, int channels, void* out,
                                   cudaStream_t stream) {
     return qf_causal_conv(is_bf16, x, x_stride, weight, bias, cu_q, tok_seq, slots, n_seqs, state, slot_stride, offset, taps,
-                          n_tokens, channels, out, 0, stream);
+                          n_tokens, channels, out, 0, 0, stream);
 }

@@ -85,6 +85,10 @@ struct TcGroups {
     const int* n_tiles;
     const float* row_scale;
     int w_rows;
+    // gate_limit > 0: the TC_SWIGLU epilogue's gate is the clamped one, g * sigmoid(gate_alpha * g) * (u + 1) with
+    // g = min(gate, limit), u = clamp(up, -limit, limit), instead of silu(gate) * up
+    float gate_limit;
+    float gate_alpha;
 };
 
 #define TC_BM 128
@@ -240,9 +244,16 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 uint32_t packed[16];
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                    const float g0 = rs * __uint_as_float(g[2 * j]), g1 = rs * __uint_as_float(g[2 * j + 1]);
-                    packed[j] = pack_bf16(g0 / (1.0f + expf(-g0)) * (rs * __uint_as_float(u[2 * j])),
-                                          g1 / (1.0f + expf(-g1)) * (rs * __uint_as_float(u[2 * j + 1])));
+                    float g0 = rs * __uint_as_float(g[2 * j]), g1 = rs * __uint_as_float(g[2 * j + 1]);
+                    float u0 = rs * __uint_as_float(u[2 * j]), u1 = rs * __uint_as_float(u[2 * j + 1]);
+                    float a = 1.0f;
+                    if (gr.gate_limit > 0.f) {
+                        const float lim = gr.gate_limit;
+                        g0 = fminf(g0, lim), g1 = fminf(g1, lim);
+                        u0 = fminf(fmaxf(u0, -lim), lim) + 1.0f, u1 = fminf(fmaxf(u1, -lim), lim) + 1.0f;
+                        a = gr.gate_alpha;
+                    }
+                    packed[j] = pack_bf16(g0 / (1.0f + expf(-a * g0)) * u0, g1 / (1.0f + expf(-a * g1)) * u1);
                 }
                 bf16* dst = out + (size_t)row * ldo + col;
                 if (col + 32 <= n_out) {
@@ -512,16 +523,19 @@ static int launch_tc_grouped(const CUtensorMap& map_a, const CUtensorMap& map_b,
 // The grouped form (see TcGroups): a [m][lda] rows sorted by group, w [n_groups * n][ldw] the groups' weights one after the
 // other (n rows each; TC_SWIGLU: n = 2 * inter, a group's gate rows then its up rows), out [m][ldo] with n columns
 // (TC_SWIGLU: inter). The plan's tiles have 128 rows; max_tiles bounds their number. The conditions of qf_tc_gemm hold.
-QF_EXPORT int qf_tc_gemm_grouped(int epilogue, const void* a, int lda, const void* w, int ldw, int n_groups, void* out, int ldo,
-                                 int m, int n, int k, const int* tile_group, const int* tile_row0, const int* offsets,
-                                 const int* n_tiles, int max_tiles, const float* row_scale, int* err, cudaStream_t stream) {
+// gate_limit > 0 (TC_SWIGLU only): the clamped gate of TcGroups instead of the SwiGLU.
+QF_EXPORT int qf_tc_gemm_grouped_gated(int epilogue, const void* a, int lda, const void* w, int ldw, int n_groups, void* out, int ldo,
+                                       int m, int n, int k, const int* tile_group, const int* tile_row0, const int* offsets,
+                                       const int* n_tiles, int max_tiles, const float* row_scale, float gate_limit, float gate_alpha,
+                                       int* err, cudaStream_t stream) {
     if (m <= 0 || n <= 0 || n_groups <= 0) return 0;
     if (k <= 0 || k % 8 || lda % 8 || ldw % 8 || ldo % 8 || !tile_group || max_tiles <= 0 || max_tiles > 65535) return (int)cudaErrorInvalidValue;
     if (((uintptr_t)a | (uintptr_t)w | (uintptr_t)out) % 16) return (int)cudaErrorInvalidValue;
     CUtensorMap map_a, map_b;
     if (!qf_make_map_bf16(&map_a, a, m, k, lda, TC_BM) || !qf_make_map_bf16(&map_b, w, (long long)n_groups * n, k, ldw, 64))
         return (int)cudaErrorNotSupported;
-    TcGroups groups{tile_group, tile_row0, offsets, n_tiles, row_scale, n};
+    TcGroups groups{tile_group, tile_row0, offsets, n_tiles, row_scale, n, gate_limit, gate_alpha};
+    if (gate_limit > 0.f && epilogue != TC_SWIGLU) return (int)cudaErrorInvalidValue;
     if (epilogue == TC_SWIGLU) {
         if (n % 2 || (n / 2) % 8) return (int)cudaErrorInvalidValue;
         const int inter = n / 2;
@@ -529,6 +543,13 @@ QF_EXPORT int qf_tc_gemm_grouped(int epilogue, const void* a, int lda, const voi
     }
     if (epilogue != TC_PLAIN || row_scale) return (int)cudaErrorInvalidValue;
     return launch_tc_grouped<TC_PLAIN>(map_a, map_b, out, m, n, k, 0, ldo, err, dim3((n + 127) / 128, max_tiles), groups, stream);
+}
+
+QF_EXPORT int qf_tc_gemm_grouped(int epilogue, const void* a, int lda, const void* w, int ldw, int n_groups, void* out, int ldo,
+                                 int m, int n, int k, const int* tile_group, const int* tile_row0, const int* offsets,
+                                 const int* n_tiles, int max_tiles, const float* row_scale, int* err, cudaStream_t stream) {
+    return qf_tc_gemm_grouped_gated(epilogue, a, lda, w, ldw, n_groups, out, ldo, m, n, k, tile_group, tile_row0, offsets, n_tiles,
+                                    max_tiles, row_scale, 0.f, 0.f, err, stream);
 }
 
 static int g_persistent = 1;

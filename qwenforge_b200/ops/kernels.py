@@ -1330,10 +1330,13 @@ def moe_gather(x: torch.Tensor, plan: MoePlan, out: torch.Tensor, scale_input: b
 
 
 def moe_combine(y: torch.Tensor, plan: MoePlan, out: torch.Tensor, scale_output: bool, extra: Optional[torch.Tensor] = None,
-                extra_gate: Optional[torch.Tensor] = None) -> None:
+                extra_gate: Optional[torch.Tensor] = None, gate_input: Optional[torch.Tensor] = None,
+                gate_weight: Optional[torch.Tensor] = None) -> None:
     """out[t] = the sum over token t's choices, in their order, of y[row of the choice] (times the routing weight with
     `scale_output`), summed in float32; y [T * top, W], out [T, W]. `extra` [T, W] is an output that every token gets beside
-    its chosen ones; it is added times sigmoid(extra_gate[t]) where `extra_gate` (float32, one logit per token) is given."""
+    its chosen ones; it is added times sigmoid(extra_gate[t]) where `extra_gate` (float32, one logit per token) is given, or
+    times sigmoid(gate_input[t] . gate_weight) where the kernel is to form that logit itself (gate_input [T, K], gate_weight
+    [K], float32 sums)."""
     _dev("y", y)
     _dev("out", out, y.dtype)
     if y.shape[0] != plan.pairs or out.shape != (plan.n_tokens, y.shape[1]):
@@ -1346,9 +1349,17 @@ def moe_combine(y: torch.Tensor, plan: MoePlan, out: torch.Tensor, scale_output:
         _dev("extra_gate", extra_gate, torch.float32)
         if extra is None or extra_gate.numel() != plan.n_tokens:
             raise KernelError("moe_combine: extra_gate holds one float32 per token and goes with extra")
+    gate_k = 0
+    if gate_weight is not None:
+        _dev("gate_input", gate_input, y.dtype)
+        _dev("gate_weight", gate_weight, y.dtype)
+        gate_k = gate_weight.numel()
+        if extra is None or extra_gate is not None or gate_input.shape != (plan.n_tokens, gate_k):
+            raise KernelError("moe_combine: gate_weight [K] goes with extra and gate_input [tokens, K], and not with extra_gate")
     _check(library("moe").qf_moe_combine_shared(_I(_is_bf16(y.dtype)), _ptr(y), _ptr(plan.dest), _ptr(plan.sorted_weight), _ptr(out),
                                                 _I(plan.n_tokens), _I(plan.top), _I(y.shape[1]), _I(int(scale_output)), _ptr(extra),
-                                                _ptr(extra_gate), _stream()), "moe_combine")
+                                                _ptr(extra_gate), _ptr(gate_input if gate_k else None),
+                                                _ptr(gate_weight if gate_k else None), _I(gate_k), _stream()), "moe_combine")
 
 
 def expert_linear(x: torch.Tensor, weight: torch.Tensor, plan: MoePlan, out: torch.Tensor, gather: bool = False) -> None:
@@ -1414,10 +1425,13 @@ def tc_gemm_grouped_takes(x: torch.Tensor, weight: torch.Tensor, plan: MoePlan, 
 
 
 def tc_gemm_grouped(epilogue: int, x: torch.Tensor, weight: torch.Tensor, plan: MoePlan, out: torch.Tensor,
-                    row_scale: Optional[torch.Tensor] = None, err: Optional[torch.Tensor] = None) -> None:
+                    row_scale: Optional[torch.Tensor] = None, err: Optional[torch.Tensor] = None,
+                    clamp: Optional[tuple] = None) -> None:
     """The experts' products on the tcgen05 tensor cores: out[row] = x[row] @ weight[expert of the row].T for rows sorted by
     expert (`plan`, tiles of 128 rows); x [T * top, K], weight [E, N, K], out [T * top, N]. TC_SWIGLU: weight[e] = [gate rows |
-    up rows], out [T * top, N / 2] = silu(s g) * (s u) with s = row_scale[row] (float32, or 1 when None)."""
+    up rows], out [T * top, N / 2] = silu(s g) * (s u) with s = row_scale[row] (float32, or 1 when None); with
+    `clamp` = (limit, alpha) the gate is the clamped one instead: min(g, limit) * sigmoid(alpha * min(g, limit)) *
+    (clamp(u, -limit, limit) + 1)."""
     _dev("x", x, torch.bfloat16, contiguous=False)
     _dev("weight", weight, torch.bfloat16)
     _dev("out", out, torch.bfloat16, contiguous=False)
@@ -1432,11 +1446,13 @@ def tc_gemm_grouped(epilogue: int, x: torch.Tensor, weight: torch.Tensor, plan: 
         _dev("row_scale", row_scale, torch.float32)
         if row_scale.numel() != plan.pairs or epilogue != TC_SWIGLU:
             raise KernelError("tc_gemm_grouped: row_scale is one float32 per row, for TC_SWIGLU")
+    if clamp is not None and (epilogue != TC_SWIGLU or not clamp[0] > 0):
+        raise KernelError("tc_gemm_grouped: the clamped gate goes with TC_SWIGLU and a positive limit")
     err = err if err is not None else _err_word_for(x.device)
-    code = library("tc_gemm").qf_tc_gemm_grouped(
+    code = library("tc_gemm").qf_tc_gemm_grouped_gated(
         _I(epilogue), _ptr(x), _I(x.stride(0)), _ptr(weight), _I(weight.stride(1)), _I(groups), _ptr(out), _I(out.stride(0)),
         _I(plan.pairs), _I(n), _I(k), _ptr(plan.tile_group), _ptr(plan.tile_row0), _ptr(plan.offsets), _ptr(plan.n_tiles),
-        _I(plan.max_tiles), _ptr(row_scale), _ptr(err), _stream())
+        _I(plan.max_tiles), _ptr(row_scale), _F(clamp[0] if clamp else 0.0), _F(clamp[1] if clamp else 0.0), _ptr(err), _stream())
     if code == 801:
         raise KernelError("tc_gemm_grouped: the driver offers no tensor-map encoder (cuTensorMapEncodeTiled)")
     _check(code, "tc_gemm_grouped")
@@ -1618,12 +1634,14 @@ CONV_MAX_TAPS = 16
 
 def causal_conv_silu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], cu_q: torch.Tensor,
                      tok_seq: torch.Tensor, slots: torch.Tensor, state: torch.Tensor, offset: int, out: torch.Tensor,
-                     activation: str = "silu") -> None:
+                     activation: str = "silu", single: bool = False) -> None:
     """A causal convolution per channel over each sequence's tokens, then silu (`activation` "none": the convolution
     alone): out[t, c] = silu(b[c] + sum_j w[c, j] *
     x[t - (taps - 1 - j), c]); inputs before the step's first token come from `state` (the sequence's last taps - 1 inputs,
     float32 [taps - 1, C] at `offset`, zeros at a sequence's start), which then takes the step's last taps - 1 inputs.
-    x: [T, C] in the activation dtype (rows may be strided); weight [C, taps], bias [C] float32; out [T, C]."""
+    x: [T, C] in the activation dtype (rows may be strided); weight [C, taps], bias [C] float32; out [T, C].
+    `single`: the caller's promise that every sequence of the step brings exactly one token; the state then moves inside
+    the same kernel."""
     _rows("x", x)
     _dev("out", out, x.dtype)
     _dev("weight", weight, torch.float32)
@@ -1642,9 +1660,9 @@ def causal_conv_silu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch
     _check(library("recurrent").qf_causal_conv(
         _I(_is_bf16(x.dtype)), _ptr(x), _I(x.stride(0)), _ptr(weight), _ptr(bias), _ptr(cu_q), _ptr(tok_seq), _ptr(slots),
         _I(cu_q.numel() - 1), _ptr(state), _LL(state.stride(0)), _LL(offset), _I(taps), _I(n), _I(c), _ptr(out),
-        _I(1 if activation == "none" else 0), _stream()), "causal_conv_silu")
+        _I(1 if activation == "none" else 0), _I(1 if single and n == cu_q.numel() - 1 else 0), _stream()), "causal_conv_silu")
 
 
-def causal_conv(x, weight, bias, cu_q, tok_seq, slots, state, offset, out) -> None:
+def causal_conv(x, weight, bias, cu_q, tok_seq, slots, state, offset, out, single: bool = False) -> None:
     """`causal_conv_silu` without the activation."""
-    causal_conv_silu(x, weight, bias, cu_q, tok_seq, slots, state, offset, out, activation="none")
+    causal_conv_silu(x, weight, bias, cu_q, tok_seq, slots, state, offset, out, activation="none", single=single)

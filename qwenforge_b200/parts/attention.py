@@ -257,7 +257,7 @@ class GqaAttention(Mixer):
         if self.conv_taps > 0:
             mixed = torch.empty((n, self.qkv_width), dtype=x.dtype, device=x.device)
             ops.causal_conv(qkv[:, :self.qkv_width], self.conv_weight, None, ctx.cu_q, ctx.tok_seq, ctx.slots, site["conv"].storage,
-                            0, mixed)
+                            0, mixed, single=ctx.is_decode and n == ctx.n_seqs)
             qkv = mixed
         q = torch.empty((n, self.q_width), dtype=x.dtype, device=x.device)
         args = ops.KvSiteArgs(kv_site.storage, kv_site.table, self.n_kv, self.head_dim)

@@ -98,7 +98,7 @@ class RoutedExperts(FeedForward):
     def forward(self, x, ctx):
         out = torch.empty_like(x)
         r = self._routed_rows(x, ctx)
-        extra = logit = None
+        extra = None
         if self.shared is not None:   # the expert that every token gets rides on the kernel that sums the chosen ones
             act = torch.empty((x.shape[0], int(self.shared["size"])), dtype=x.dtype, device=x.device)
             if self.gate == "clamped":
@@ -106,9 +106,9 @@ class RoutedExperts(FeedForward):
             else:
                 ops.swiglu(ops.linear_rows(x, self.shared_gate_up), act)
             extra = ops.linear_rows(act, self.shared_down)
-            if self.shared_logit is not None:
-                logit = ops.linear_rows(x, self.shared_logit, out_dtype=torch.float32)
-        ops.moe_combine(r.rows, self._plan, out, r.row_weight is not None, extra, logit)
+        # (the shared expert's gate, one logit per token, is formed inside the kernel that sums)
+        ops.moe_combine(r.rows, self._plan, out, r.row_weight is not None, extra, None, x if self.shared_logit is not None else None,
+                        self.shared_logit.view(-1) if self.shared_logit is not None else None)
         return out
 
     def _routed_rows(self, x, ctx) -> RowSum:
@@ -125,12 +125,20 @@ class RoutedExperts(FeedForward):
             plan = ops.moe_plan(ops.linear(x, self.router, out_dtype=torch.float32), self.top, soft, renorm, tile_rows, bias=self.bias)
         self._plan = plan
         if self.gate == "clamped":
-            # the rows are read through the plan's row map; both halves in one product, then the clamped gate
+            act = torch.empty((plan.pairs, self.inter), dtype=x.dtype, device=x.device)
+            rows = torch.empty((plan.pairs, self.hidden), dtype=x.dtype, device=x.device)
+            if tile_rows == ops.kernels.GROUP_LARGE_TILE_ROWS and ops.tc_gemm_grouped_takes(rows, self.gate_up, plan, ops.TC_SWIGLU) \
+                    and ops.tc_gemm_grouped_takes(act, self.down, plan):
+                # long steps: both products on the tcgen05 tensor cores, the clamped gate in the first one's epilogue
+                ops.moe_gather(x, plan, rows, False)
+                ops.tc_gemm_grouped(ops.TC_SWIGLU, rows, self.gate_up, plan, act, None, ctx.err, clamp=(self.limit, self.alpha))
+                y = torch.empty_like(rows)
+                ops.tc_gemm_grouped(ops.TC_PLAIN, act, self.down, plan, y, None, ctx.err)
+                return RowSum(y, plan.dest, self.top, plan.sorted_weight)
+            # otherwise the rows are read through the plan's row map; both halves in one product, then the clamped gate
             gate_up = torch.empty((plan.pairs, 2 * self.inter), dtype=x.dtype, device=x.device)
             ops.expert_linear(x, self.gate_up, plan, gate_up, gather=True)
-            act = torch.empty((plan.pairs, self.inter), dtype=x.dtype, device=x.device)
             ops.clamped_glu(gate_up, self.limit, self.alpha, act)
-            rows = torch.empty((plan.pairs, self.hidden), dtype=x.dtype, device=x.device)
             ops.expert_linear(act, self.down, plan, rows)
             return RowSum(rows, plan.dest, self.top, plan.sorted_weight)
         # A weight on the expert's input moves behind its first product (G (w h) = w (G h), and the same for U), where it

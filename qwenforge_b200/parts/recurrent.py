@@ -148,7 +148,7 @@ class StateSpace(Mixer):
         dt_pre = ops.linear_rows(x, self.dt_weight, out_dtype=torch.float32)          # [T, H], float32 sums
         xbc = torch.empty((n, self.channels), dtype=x.dtype, device=x.device)
         ops.causal_conv_silu(main[:, self.inner:], self.conv_weight, self.conv_bias, ctx.cu_q, ctx.tok_seq, ctx.slots,
-                             site.storage, self.conv_offset, xbc)
+                             site.storage, self.conv_offset, xbc, single=ctx.is_decode and n == ctx.n_seqs)
         decay, take = torch.empty((n, h), **f32), torch.empty((n, h), **f32)
         ops.decay_gates(dt_pre, self.dt_bias, self.rate_log, decay, take)
         y = torch.empty((n, self.inner), **f32)

@@ -78,7 +78,8 @@ class TokenShift(Part):
 
     def forward(self, h: torch.Tensor, ctx, site) -> torch.Tensor:
         out = torch.empty_like(h)
-        ops.causal_conv(h, self.taps, None, ctx.cu_q, ctx.tok_seq, ctx.slots, site.storage, 0, out)
+        ops.causal_conv(h, self.taps, None, ctx.cu_q, ctx.tok_seq, ctx.slots, site.storage, 0, out,
+                        single=ctx.is_decode and h.shape[0] == ctx.n_seqs)
         return out
 
 

@@ -254,13 +254,17 @@ def expert_gate_takes(x, weight, plan):
     return False
 
 
-def tc_gemm_grouped(epilogue, x, weight, plan, out, row_scale=None, err=None):
+def tc_gemm_grouped(epilogue, x, weight, plan, out, row_scale=None, err=None, clamp=None):
     y = torch.einsum("rk,rnk->rn", _f(x), _f(weight)[plan.row_expert])
     if epilogue == 1:   # gate rows then up rows, a scale on both before the gate
         inter = y.shape[1] // 2
         s = _f(row_scale)[:, None] if row_scale is not None else 1.0
         g, u = y[:, :inter] * s, y[:, inter:] * s
-        y = g * torch.sigmoid(g) * u
+        if clamp is not None:
+            g, u = g.clamp(max=clamp[0]), u.clamp(min=-clamp[0], max=clamp[0]) + 1
+            y = g * torch.sigmoid(clamp[1] * g) * u
+        else:
+            y = g * torch.sigmoid(g) * u
     out.copy_(y.to(out.dtype))
 
 
@@ -298,7 +302,9 @@ def moe_gather(x, plan, out, scale_input):
     out.copy_(rows.to(out.dtype))
 
 
-def moe_combine(y, plan, out, scale_output, extra=None, extra_gate=None):
+def moe_combine(y, plan, out, scale_output, extra=None, extra_gate=None, gate_input=None, gate_weight=None):
+    if gate_weight is not None:
+        extra_gate = _f(gate_input) @ _f(gate_weight)
     rows = _f(y)
     if scale_output:
         rows = rows * _f(plan.sorted_weight)[:, None]
@@ -401,7 +407,7 @@ def gated_group_norm(y, gate, weight, eps, out, n_parts, n_heads, gate_kind, gat
     out.copy_(z.to(out.dtype))
 
 
-def causal_conv_silu(x, weight, bias, cu_q, tok_seq, slots, state, offset, out, activation="silu"):
+def causal_conv_silu(x, weight, bias, cu_q, tok_seq, slots, state, offset, out, activation="silu", single=False):
     n, c = x.shape
     taps = weight.shape[1]
     for s in range(cu_q.numel() - 1):
@@ -419,7 +425,7 @@ def causal_conv_silu(x, weight, bias, cu_q, tok_seq, slots, state, offset, out, 
             state[slot, offset:offset + (taps - 1) * c] = padded[padded.shape[0] - (taps - 1):].reshape(-1).float()
 
 
-def causal_conv(x, weight, bias, cu_q, tok_seq, slots, state, offset, out):
+def causal_conv(x, weight, bias, cu_q, tok_seq, slots, state, offset, out, single=False):
     causal_conv_silu(x, weight, bias, cu_q, tok_seq, slots, state, offset, out, activation="none")
 
 

@@ -121,13 +121,15 @@ def test_convolution_without_activation(dtype, taps, channels):
     g = torch.Generator().manual_seed(taps)
     weight = rand(g, channels, taps)
     states = [torch.zeros(3, 5 + max(taps - 1, 1) * channels, device=DEV) for _ in range(2)]
-    for spans, slots in (([(0, 6), (0, 1), (0, 3)], [2, -1, 0]), ([(6, 1), (3, 2)], [2, 0]), ([(7, 5), (5, 1)], [2, 0])):
+    for spans, slots in (([(0, 6), (0, 1), (0, 3)], [2, -1, 0]), ([(6, 1), (3, 2)], [2, 0]), ([(7, 1), (5, 1), (0, 1)], [2, 0, -1]),
+                         ([(8, 1), (6, 1)], [2, 0]), ([(9, 1), (7, 1)], [2, 0]), ([(10, 5), (8, 1)], [2, 0]), ([(0, 1)], [1]), ([(1, 1)], [1])):
         batch = Batch(slots, spans)
         wide = rand(g, batch.n_tokens, channels + 3, dtype=dtype)
         outs = []
         for fn, state in ((ops.causal_conv, states[0]), (refs.causal_conv, states[1])):
             out = torch.empty(batch.n_tokens, channels, dtype=dtype, device=DEV)
-            fn(wide[:, :channels], weight, None, batch.cu_q, batch.tok_seq, batch.slots, state, 5, out)
+            # steps of one token per sequence move the kept inputs inside the same kernel
+            fn(wide[:, :channels], weight, None, batch.cu_q, batch.tok_seq, batch.slots, state, 5, out, single=batch.max_q_len == 1)
             outs.append(out)
         close(outs[0], outs[1], dtype, "conv", bf16=1e-2)
         assert max_err(states[0], states[1]) < 1e-6
@@ -286,6 +288,35 @@ def test_router_bias_softmax_over_the_chosen_and_the_shared_expert(dtype):
             ops.moe_combine(y, plan, out, True, e, lg)
             refs.moe_combine(y, plan, want_out, True, e, lg)
             close(out, want_out, dtype, "combine", bf16=1e-2)
+        gate_weight = rand(g, 48, dtype=dtype, spread=0.3)      # the gate's logit formed inside the kernel
+        ops.moe_combine(y, plan, out, True, extra, None, x, gate_weight)
+        refs.moe_combine(y, plan, want_out, True, extra, None, x, gate_weight)
+        close(out, want_out, dtype, "combine with its own gate", bf16=1e-2)
+
+
+def test_clamped_gate_in_the_grouped_tensor_core_product():
+    """A step long enough for tiles of 128 rows: the experts' first product with the clamped gate in its epilogue against
+    the reference, with limits that most sums exceed and limits that none does."""
+    from qwenforge_b200 import ops
+    g = torch.Generator().manual_seed(5)
+    tokens, experts, top, width, inter = 1500, 4, 2, 128, 96
+    x, router = rand(g, tokens, width, dtype=torch.bfloat16), rand(g, experts, width, dtype=torch.bfloat16, spread=0.3)
+    weight = rand(g, experts, 2 * inter, width, dtype=torch.bfloat16, spread=0.2)
+    plan = ops.moe_plan(ops.linear(x, router, out_dtype=torch.float32), top, True, True, 128)
+    rows = torch.empty(tokens * top, width, dtype=torch.bfloat16, device=DEV)
+    ops.moe_gather(x, plan, rows, False)
+    assert ops.tc_gemm_grouped_takes(rows, weight, plan, ops.TC_SWIGLU)
+    experts_of = torch.empty(tokens * top, dtype=torch.long, device=DEV)
+    experts_of[plan.dest.long()] = plan.pair_expert.long()
+    class Routing:
+        row_expert = experts_of
+    for limit in (0.5, 50.0):
+        out, want = (torch.empty(tokens * top, inter, dtype=torch.bfloat16, device=DEV) for _ in range(2))
+        err = torch.zeros(1, dtype=torch.int32, device=DEV)
+        ops.tc_gemm_grouped(ops.TC_SWIGLU, rows, weight, plan, out, None, err, clamp=(limit, 1.702))
+        refs.tc_gemm_grouped(1, rows, weight, Routing, want, clamp=(limit, 1.702))
+        assert int(err) == 0
+        close(out, want, torch.bfloat16, f"limit {limit}", bf16=2e-2)
 
 
 # ------------------------------------------------------------------------------------------------ the model
