@@ -33,6 +33,7 @@ struct GroupedArgs {
     int max_tiles;
     const int* a_rows;       // null: row r of A is row r
     const float* row_scale;  // gated tiles: a factor per row on both halves before the gate (null: 1)
+    float gate_limit, gate_alpha;   // gated tiles, gate_limit > 0: the clamped gate min(g, limit) sigmoid(alpha g) (clamp(u) + 1)
 };
 
 // Which group and which rows this block has; false if it has none.
@@ -201,9 +202,18 @@ grouped_gemm_mma_kernel(GroupedArgs g) {
 #pragma unroll
                 for (int j = 0; j < 2; ++j) {
                     const int gn = n0 + 16 * wx + 8 * j + 2 * (lane & 3);
-                    const float g0 = s * acc[i][j][2 * half], g1 = s * acc[i][j][2 * half + 1];
-                    const float v0 = g0 / (1.0f + expf(-g0)) * (s * acc[i][2 + j][2 * half]);
-                    const float v1 = g1 / (1.0f + expf(-g1)) * (s * acc[i][2 + j][2 * half + 1]);
+                    float g0 = s * acc[i][j][2 * half], g1 = s * acc[i][j][2 * half + 1];
+                    float u0 = s * acc[i][2 + j][2 * half], u1 = s * acc[i][2 + j][2 * half + 1], slope = 1.f;
+                    if (g.gate_limit > 0.f) {   // both halves clamped, the slope inside the sigmoid, one added to the up half
+                        const float limit = g.gate_limit;
+                        g0 = fminf(g0, limit);
+                        g1 = fminf(g1, limit);
+                        u0 = fminf(fmaxf(u0, -limit), limit) + 1.0f;
+                        u1 = fminf(fmaxf(u1, -limit), limit) + 1.0f;
+                        slope = g.gate_alpha;
+                    }
+                    const float v0 = g0 / (1.0f + expf(-slope * g0)) * u0;
+                    const float v1 = g1 / (1.0f + expf(-slope * g1)) * u1;
                     bf16* dst = C + (long long)gm * g.ldc + gn;
                     if (gn + 1 < N && (((uintptr_t)dst) & 3) == 0) *reinterpret_cast<uint32_t*>(dst) = pack_bf16(v0, v1);
                     else {
@@ -335,14 +345,15 @@ static bool mma_takes(const GroupedArgs& g) {
 // See the top of the file. tile_group == null: uniform groups over all rows; else the ragged plan (a_group_cols and
 // c_group_cols are then not used), whose tiles have `tile_rows` rows: 64, or 128 for the large tile (bfloat16 with aligned
 // operands only: see qf_grouped_gemm_large_takes). A, W and C share the activation dtype; a_rows: see the top.
-QF_EXPORT int qf_grouped_gemm(int is_bf16, const void* a, long long lda, long long a_group_cols, const void* w,
-                              long long w_group_stride, long long ldw, void* c, long long ldc, long long c_group_cols,
-                              int rows, int n, int k, int n_groups, const int* tile_group, const int* tile_row0,
-                              const int* offsets, const int* n_tiles, int max_tiles, int tile_rows, const int* a_rows,
-                              int gated, const float* row_scale, cudaStream_t stream) {
+// gate_limit > 0 (gated products only): the clamped form of the gate with this limit and the slope gate_alpha.
+QF_EXPORT int qf_grouped_gemm_gate(int is_bf16, const void* a, long long lda, long long a_group_cols, const void* w,
+                                   long long w_group_stride, long long ldw, void* c, long long ldc, long long c_group_cols,
+                                   int rows, int n, int k, int n_groups, const int* tile_group, const int* tile_row0,
+                                   const int* offsets, const int* n_tiles, int max_tiles, int tile_rows, const int* a_rows,
+                                   int gated, const float* row_scale, float gate_limit, float gate_alpha, cudaStream_t stream) {
     if (rows <= 0 || n <= 0 || n_groups <= 0) return 0;
     GroupedArgs g{a, lda, a_group_cols, w, w_group_stride, ldw, c, ldc, c_group_cols, rows, n, k, n_groups,
-                  tile_group, tile_row0, offsets, n_tiles, max_tiles, a_rows, row_scale};
+                  tile_group, tile_row0, offsets, n_tiles, max_tiles, a_rows, row_scale, gate_limit, gate_alpha};
     if (gated) {  // n = columns of the result (half of a group's weight rows); the small tensor-core tile only
         if (!is_bf16 || !mma_takes(g) || (tile_group && tile_rows != QF_GROUP_BM)) return (int)cudaErrorInvalidValue;
         const dim3 grid((n + GG_BN / 2 - 1) / (GG_BN / 2), tile_group ? max_tiles : (rows + QF_GROUP_BM - 1) / QF_GROUP_BM, tile_group ? 1 : n_groups);
@@ -365,6 +376,16 @@ QF_EXPORT int qf_grouped_gemm(int is_bf16, const void* a, long long lda, long lo
     if (is_bf16 && mma_takes(g)) return (int)launch_pdl(grouped_gemm_mma_kernel<false>, grid, dim3(128), 0, stream, g);
     if (is_bf16) return (int)launch_pdl(grouped_gemm_plain_kernel<bf16>, grid, dim3(256), 0, stream, g);
     return (int)launch_pdl(grouped_gemm_plain_kernel<float>, grid, dim3(256), 0, stream, g);
+}
+
+QF_EXPORT int qf_grouped_gemm(int is_bf16, const void* a, long long lda, long long a_group_cols, const void* w,
+                              long long w_group_stride, long long ldw, void* c, long long ldc, long long c_group_cols,
+                              int rows, int n, int k, int n_groups, const int* tile_group, const int* tile_row0,
+                              const int* offsets, const int* n_tiles, int max_tiles, int tile_rows, const int* a_rows,
+                              int gated, const float* row_scale, cudaStream_t stream) {
+    return qf_grouped_gemm_gate(is_bf16, a, lda, a_group_cols, w, w_group_stride, ldw, c, ldc, c_group_cols, rows, n, k, n_groups,
+                                tile_group, tile_row0, offsets, n_tiles, max_tiles, tile_rows, a_rows, gated, row_scale, 0.f, 0.f,
+                                stream);
 }
 
 // Whether a ragged product of these operands may use tiles of 128 rows (the plan has to be cut accordingly).

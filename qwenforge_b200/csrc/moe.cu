@@ -258,13 +258,59 @@ moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ dest, const 
     if (t >= n_tokens) return;
     // an output that every token gets beside its chosen ones (`extra`), under a sigmoid gate of one logit per token: given,
     // or formed here as the token's row times the gate's weights (float32 sums in a fixed order)
+    constexpr int V = 16 / (int)sizeof(T);
     float share = extra ? 1.f : 0.f;
     if (extra && extra_gate) share = 1.f / (1.f + expf(-extra_gate[t]));
     if (extra && gate_weight) {
         float sum = 0.f;
-        for (int c = threadIdx.x; c < gate_k; c += blockDim.x)
-            sum = fmaf(Num<T>::to_f(gate_input[(size_t)t * gate_k + c]), Num<T>::to_f(gate_weight[c]), sum);
+        if (gate_k % V == 0 && (((uintptr_t)gate_input | (uintptr_t)gate_weight) & 15) == 0) {
+            for (int c = threadIdx.x * V; c < gate_k; c += blockDim.x * V) {   // 16 bytes of the row and of the weights at a time
+                T a[V], b[V];
+                *reinterpret_cast<uint4*>(a) = *reinterpret_cast<const uint4*>(gate_input + (size_t)t * gate_k + c);
+                *reinterpret_cast<uint4*>(b) = *reinterpret_cast<const uint4*>(gate_weight + c);
+#pragma unroll
+                for (int v = 0; v < V; ++v) sum = fmaf(Num<T>::to_f(a[v]), Num<T>::to_f(b[v]), sum);
+            }
+        } else {
+            for (int c = threadIdx.x; c < gate_k; c += blockDim.x)
+                sum = fmaf(Num<T>::to_f(gate_input[(size_t)t * gate_k + c]), Num<T>::to_f(gate_weight[c]), sum);
+        }
         share = 1.f / (1.f + expf(-block_sum(sum, scratch)));
+    }
+    if (width % V == 0 && top <= MOE_MAX_TOP && (((uintptr_t)y | (uintptr_t)out | (uintptr_t)extra) & 15) == 0) {
+        // the same sums, 16 bytes of every row at a time; the rows and their weights are looked up once
+        int row[MOE_MAX_TOP];
+        float rw[MOE_MAX_TOP];
+#pragma unroll
+        for (int k = 0; k < MOE_MAX_TOP; ++k)
+            if (k < top) {
+                row[k] = dest[t * top + k];
+                rw[k] = scale_output ? sorted_weight[row[k]] : 1.f;
+            }
+        for (int c = threadIdx.x * V; c < width; c += blockDim.x * V) {
+            float sum[V];
+#pragma unroll
+            for (int v = 0; v < V; ++v) sum[v] = 0.f;
+#pragma unroll
+            for (int k = 0; k < MOE_MAX_TOP; ++k)
+                if (k < top) {
+                    T in[V];
+                    *reinterpret_cast<uint4*>(in) = *reinterpret_cast<const uint4*>(y + (size_t)row[k] * width + c);
+#pragma unroll
+                    for (int v = 0; v < V; ++v) sum[v] += scale_output ? Num<T>::to_f(in[v]) * rw[k] : Num<T>::to_f(in[v]);
+                }
+            T res[V];
+            if (extra) {
+                T in[V];
+                *reinterpret_cast<uint4*>(in) = *reinterpret_cast<const uint4*>(extra + (size_t)t * width + c);
+#pragma unroll
+                for (int v = 0; v < V; ++v) sum[v] = fmaf(share, Num<T>::to_f(in[v]), sum[v]);
+            }
+#pragma unroll
+            for (int v = 0; v < V; ++v) res[v] = Num<T>::from_f(sum[v]);
+            *reinterpret_cast<uint4*>(out + (size_t)t * width + c) = *reinterpret_cast<const uint4*>(res);
+        }
+        return;
     }
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
         float sum = 0.f;

@@ -369,6 +369,51 @@ QF_EXPORT int qf_add_dyt_norm(int is_bf16, float* hidden, const void* a, const v
                    : launch_dyt<float>(hidden, a, b, weight, bias, alpha, out, rows, width, stream);
 }
 
+// The same norm for a step of ONE token per sequence, with a token shift behind it in the same kernel: beside `out` it writes
+//   shifted = taps[c][0] * (the row's previous out, kept per slot in `state`, zeros for slot < 0) + taps[c][1] * out
+// and leaves out (as rounded to the activation type) in the state: what a two-tap causal convolution over `out` would give
+// and keep, product by product (fmaf(taps[c][0], previous, 0), then fmaf(taps[c][1], out, that)).
+template <typename T>
+__global__ void __launch_bounds__(256)
+add_dyt_norm_shift_kernel(float* __restrict__ hidden, const T* __restrict__ a, const T* __restrict__ b, const T* __restrict__ weight,
+                          const T* __restrict__ bias, float alpha, T* __restrict__ out, const float* __restrict__ taps,
+                          const int* __restrict__ slots, float* __restrict__ state, long long slot_stride, T* __restrict__ shifted,
+                          size_t total, int width) {
+    grid_chain_entry();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        float v = hidden[i];
+        if (a || b) {
+            v += (a ? Num<T>::to_f(a[i]) : 0.f) + (b ? Num<T>::to_f(b[i]) : 0.f);
+            hidden[i] = v;
+        }
+        const int c = (int)(i % width), slot = slots[i / width];
+        const T h = Num<T>::from_f(fmaf(tanhf(alpha * v), Num<T>::to_f(weight[c]), Num<T>::to_f(bias[c])));
+        out[i] = h;
+        const float u = Num<T>::to_f(h);
+        float* kept = slot >= 0 ? state + slot * slot_stride : nullptr;
+        float z = fmaf(taps[2 * c], kept ? kept[c] : 0.f, 0.f);
+        z = fmaf(taps[2 * c + 1], u, z);
+        shifted[i] = Num<T>::from_f(z);
+        if (kept) kept[c] = u;
+    }
+}
+
+// rows: one token of every sequence; slots int32 [rows]; taps float32 [width][2] (the older input's first); state float32, one
+// row of `slot_stride` floats per slot whose first `width` hold the previous out.
+QF_EXPORT int qf_add_dyt_norm_shift(int is_bf16, float* hidden, const void* a, const void* b, const void* weight, const void* bias,
+                                    float alpha, void* out, const float* taps, const int* slots, float* state, long long slot_stride,
+                                    void* shifted, int rows, int width, cudaStream_t stream) {
+    if (rows <= 0 || width <= 0) return 0;
+    const size_t total = (size_t)rows * width;
+    if (is_bf16)
+        return (int)launch_pdl(add_dyt_norm_shift_kernel<bf16>, dim3(elementwise_blocks(total)), dim3(256), 0, stream, hidden,
+                               (const bf16*)a, (const bf16*)b, (const bf16*)weight, (const bf16*)bias, alpha, (bf16*)out, taps, slots,
+                               state, slot_stride, (bf16*)shifted, total, width);
+    return (int)launch_pdl(add_dyt_norm_shift_kernel<float>, dim3(elementwise_blocks(total)), dim3(256), 0, stream, hidden,
+                           (const float*)a, (const float*)b, (const float*)weight, (const float*)bias, alpha, (float*)out, taps, slots,
+                           state, slot_stride, (float*)shifted, total, width);
+}
+
 // hidden += (a + b): two pending outputs of one layer, summed with each other first, then into the float32 stream.
 template <typename T>
 __global__ void __launch_bounds__(256)

@@ -437,6 +437,74 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ x, int x_stride, c
     out[(size_t)t * channels + c] = Num<T>::from_f(plain ? z : z / (1.f + expf(-z)));
 }
 
+// The same convolution for long steps: a thread takes 16 bytes of channels and a run of CONV_RUN consecutive tokens, keeps
+// the last TAPS - 1 inputs in registers as it walks down the run, and fetches them afresh (from the state, or zeros) where a
+// sequence begins inside the run. Every output is the same chain of fused multiply-adds, oldest input first, as in the
+// kernel of one thread per (token, channel): the two agree bit for bit.
+#define CONV_RUN 8
+
+template <typename T, int TAPS>
+__global__ void __launch_bounds__(128)
+causal_conv_run_kernel(const T* __restrict__ x, int x_stride, const float* __restrict__ weight, const float* __restrict__ bias,
+                       const int* __restrict__ cu_q, const int* __restrict__ tok_seq, const int* __restrict__ slots,
+                       const float* __restrict__ state, long long slot_stride, long long offset, int n_tokens, int channels,
+                       T* __restrict__ out, int plain) {
+    constexpr int V = 16 / (int)sizeof(T);
+    constexpr int H = TAPS > 1 ? TAPS - 1 : 1;
+    grid_chain_entry();
+    const int groups = channels / V;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int n_runs = (n_tokens + CONV_RUN - 1) / CONV_RUN;
+    if (i >= (long long)n_runs * groups) return;
+    const int t0 = (int)(i / groups) * CONV_RUN, c0 = (int)(i % groups) * V;
+    float w[V][TAPS], b[V], hist[H][V];
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+        b[v] = bias ? bias[c0 + v] : 0.f;
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) w[v][j] = weight[(size_t)(c0 + v) * TAPS + j];
+    }
+#pragma unroll
+    for (int k = 0; k < CONV_RUN; ++k) {
+        const int t = t0 + k;
+        if (t >= n_tokens) break;
+        const int seq = tok_seq[t], at = t - cu_q[seq];
+        if (TAPS > 1 && (k == 0 || at == 0)) {
+            const int slot = slots[seq];
+            const float* before = slot >= 0 ? state + slot * slot_stride + offset : nullptr;
+#pragma unroll
+            for (int r = 0; r < TAPS - 1; ++r) {   // hist[r]: the input TAPS - 1 - r tokens back
+                const int back = TAPS - 1 - r;
+                if (at - back >= 0) {
+                    T in[V];
+                    *reinterpret_cast<uint4*>(in) = *reinterpret_cast<const uint4*>(x + (size_t)(t - back) * x_stride + c0);
+#pragma unroll
+                    for (int v = 0; v < V; ++v) hist[r][v] = Num<T>::to_f(in[v]);
+                } else {
+#pragma unroll
+                    for (int v = 0; v < V; ++v)
+                        hist[r][v] = before ? before[(size_t)(TAPS - 1 + at - back) * channels + c0 + v] : 0.f;
+                }
+            }
+        }
+        T in[V], res[V];
+        *reinterpret_cast<uint4*>(in) = *reinterpret_cast<const uint4*>(x + (size_t)t * x_stride + c0);
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+            const float u = Num<T>::to_f(in[v]);
+            float z = b[v];
+#pragma unroll
+            for (int r = 0; r < TAPS - 1; ++r) z = fmaf(w[v][r], hist[r][v], z);
+            z = fmaf(w[v][TAPS - 1], u, z);
+            res[v] = Num<T>::from_f(plain ? z : z / (1.f + expf(-z)));
+#pragma unroll
+            for (int r = 0; r + 1 < TAPS - 1; ++r) hist[r][v] = hist[r + 1][v];
+            if (TAPS > 1) hist[H - 1][v] = u;
+        }
+        *reinterpret_cast<uint4*>(out + (size_t)t * channels + c0) = *reinterpret_cast<const uint4*>(res);
+    }
+}
+
 template <typename T>
 __global__ void conv_state_kernel(const T* __restrict__ x, int x_stride, const int* __restrict__ cu_q,
                                   const int* __restrict__ slots, int n_seqs, float* __restrict__ state, long long slot_stride,
@@ -461,9 +529,22 @@ static int launch_conv(const void* x, int x_stride, const float* weight, const f
                        const int* slots, int n_seqs, float* state, long long slot_stride, long long offset, int taps,
                        int n_tokens, int channels, void* out, int plain, int single, cudaStream_t stream) {
     const long long total = (long long)n_tokens * channels;
-    cudaError_t e = launch_pdl(causal_conv_silu_kernel<T>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream,
-                               (const T*)x, x_stride, weight, bias, cu_q, tok_seq, slots, state, slot_stride, offset,
-                               taps, n_tokens, channels, (T*)out, plain, single);
+    constexpr int V = 16 / (int)sizeof(T);
+    const bool runs = !single && n_tokens >= 4 * CONV_RUN && (taps == 2 || taps == 3 || taps == 4) && channels % V == 0 &&
+                      x_stride % V == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0;
+    cudaError_t e;
+    if (runs) {
+        const long long items = (long long)((n_tokens + CONV_RUN - 1) / CONV_RUN) * (channels / V);
+        const dim3 grid((unsigned)((items + 127) / 128)), block(128);
+#define QF_CONV_RUN(TAPS) launch_pdl(causal_conv_run_kernel<T, TAPS>, grid, block, 0, stream, (const T*)x, x_stride, weight, bias, \
+                                     cu_q, tok_seq, slots, (const float*)state, slot_stride, offset, n_tokens, channels, (T*)out, plain)
+        e = taps == 2 ? QF_CONV_RUN(2) : taps == 3 ? QF_CONV_RUN(3) : QF_CONV_RUN(4);
+#undef QF_CONV_RUN
+    } else {
+        e = launch_pdl(causal_conv_silu_kernel<T>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream,
+                       (const T*)x, x_stride, weight, bias, cu_q, tok_seq, slots, state, slot_stride, offset,
+                       taps, n_tokens, channels, (T*)out, plain, single);
+    }
     if (e != cudaSuccess || taps <= 1 || single) return (int)e;
     const long long pairs = (long long)n_seqs * channels;
     // launched the ordinary way: it must not start before every block of the convolution has read the old state

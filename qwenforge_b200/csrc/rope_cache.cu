@@ -341,14 +341,19 @@ QF_EXPORT int qf_rope_norm_cache_write(int is_bf16, const void* qkv, const void*
 
 // Rows of whole blocks beside a cache: once the last position of a block of `pool` positions has been written, the block's
 // row in a second cache (`rows`: one row per block, addressed like positions) becomes the mean of the block's keys and the
-// mean of its values AS THE CACHE HOLDS THEM (float32 sums in rising order of the positions, divided by `pool`, rounded to
-// the cache's type). A block of threads per (candidate block of the step, sequence): a step of q tokens that starts at
-// position p completes the blocks floor(p / pool) .. floor((p + q) / pool) - 1.
+// mean of its values AS THE CACHE HOLDS THEM (float32 sums, divided by `pool`, rounded to the cache's type). A block of
+// threads per (candidate block of the step, sequence, plane of one kv head's keys or values): a step of q tokens that starts
+// at position p completes the blocks floor(p / pool) .. floor((p + q) / pool) - 1. The block's positions are dealt to
+// POOL_PARTS groups of threads in turn (position j to group j % POOL_PARTS, each summing its own in rising order), and the
+// groups' sums are added in the groups' order: one fixed order of additions for a block, whatever the step that completes it.
+#define POOL_PARTS 4
+
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(POOL_PARTS * 64)
 pool_cache_kernel(const int* __restrict__ cu_q, const int* __restrict__ tok_pos, const int* __restrict__ slots, KvSite<T> site,
                   KvSite<T> rows, int pool, int* err) {
     grid_chain_entry();
+    extern __shared__ float pool_parts[];   // [POOL_PARTS][head_dim], and one flag per part behind them
     const int seq = blockIdx.y, slot = slots[seq];
     if (slot < 0) return;
     const int begin = cu_q[seq], len = cu_q[seq + 1] - begin;
@@ -356,19 +361,36 @@ pool_cache_kernel(const int* __restrict__ cu_q, const int* __restrict__ tok_pos,
     const int start = tok_pos[begin];
     const int b = start / pool + blockIdx.x;
     if ((long long)(b + 1) * pool > (long long)start + len) return;   // not complete after this step
-    const int D = site.head_dim, per_plane = site.kv_heads * D;
-    for (int i = threadIdx.x; i < 2 * per_plane; i += blockDim.x) {
-        const int which = i / per_plane, h = (i % per_plane) / D, d = i % D;
+    const int D = site.head_dim;
+    const int which = blockIdx.z / site.kv_heads, h = blockIdx.z % site.kv_heads;
+    const int lanes = blockDim.x / POOL_PARTS, part = threadIdx.x / lanes, lane = threadIdx.x % lanes;
+    int* missing = reinterpret_cast<int*>(pool_parts + POOL_PARTS * D);
+    if (threadIdx.x == 0) *missing = 0;
+    __syncthreads();
+    for (int d0 = 0; d0 < D; d0 += lanes) {
+        const int d = d0 + lane;
         float sum = 0.f;
         bool held = true;
-        for (int j = 0; j < pool; ++j) {
+#pragma unroll 4
+        for (int j = part; j < pool; j += POOL_PARTS) {
             const T* src = kv_row(site, slot, b * pool + j, h, which);
-            if (src) sum += Num<T>::to_f(src[d]);
+            if (src) { if (d < D) sum += Num<T>::to_f(src[d]); }
             else held = false;
         }
-        T* dst = kv_row(rows, slot, b, h, which);
-        if (dst && held) dst[d] = Num<T>::from_f(sum / (float)pool);
-        else if (d == 0) atomicOr(err, QF_ERR_NO_PAGE);
+        if (!held) *missing = 1;
+        if (d < D) pool_parts[part * D + d] = sum;
+    }
+    __syncthreads();
+    T* dst = kv_row(rows, slot, b, h, which);
+    if (!dst || *missing) {
+        if (threadIdx.x == 0) atomicOr(err, QF_ERR_NO_PAGE);
+        return;
+    }
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float sum = pool_parts[d];
+#pragma unroll
+        for (int p = 1; p < POOL_PARTS; ++p) sum += pool_parts[p * D + d];
+        dst[d] = Num<T>::from_f(sum / (float)pool);
     }
 }
 
@@ -379,13 +401,14 @@ QF_EXPORT int qf_pool_cache_write(int is_bf16, const int* cu_q, const int* tok_p
                                   int max_blocks, int* err, cudaStream_t stream) {
     if (n_seqs <= 0 || max_blocks <= 0) return 0;
     if (pool <= 0) return (int)cudaErrorInvalidValue;
-    const dim3 grid(max_blocks, n_seqs), block(128);
+    const dim3 grid(max_blocks, n_seqs, 2 * kv_heads), block(POOL_PARTS * (head_dim <= 32 ? 32 : 64));
+    const size_t smem = (size_t)POOL_PARTS * head_dim * sizeof(float) + sizeof(int);
     if (is_bf16)
-        return (int)launch_pdl(pool_cache_kernel<bf16>, grid, block, 0, stream, cu_q, tok_pos, slots,
+        return (int)launch_pdl(pool_cache_kernel<bf16>, grid, block, smem, stream, cu_q, tok_pos, slots,
                                KvSite<bf16>{(bf16*)base, table, page_elems, table_stride, kv_heads, head_dim},
                                KvSite<bf16>{(bf16*)rows_base, rows_table, rows_page_elems, rows_table_stride, kv_heads, head_dim},
                                pool, err);
-    return (int)launch_pdl(pool_cache_kernel<float>, grid, block, 0, stream, cu_q, tok_pos, slots,
+    return (int)launch_pdl(pool_cache_kernel<float>, grid, block, smem, stream, cu_q, tok_pos, slots,
                            KvSite<float>{(float*)base, table, page_elems, table_stride, kv_heads, head_dim},
                            KvSite<float>{(float*)rows_base, rows_table, rows_page_elems, rows_table_stride, kv_heads, head_dim},
                            pool, err);

@@ -956,6 +956,36 @@ def add_dyt_norm(hidden: torch.Tensor, a: Optional[torch.Tensor], b: Optional[to
                                            _F(alpha), _ptr(out), _I(rows), _I(width), _stream()), "add_dyt_norm")
 
 
+def add_dyt_norm_shift(hidden: torch.Tensor, a: Optional[torch.Tensor], b: Optional[torch.Tensor], weight: torch.Tensor,
+                       bias: torch.Tensor, alpha: float, out: torch.Tensor, taps: torch.Tensor, slots: torch.Tensor,
+                       state: torch.Tensor, shifted: torch.Tensor) -> None:
+    """`add_dyt_norm` for a step of one token per sequence with a token shift in the same kernel:
+    shifted = taps[:, 0] * previous out of the row's slot (state[slot, :W], zeros for slot < 0) + taps[:, 1] * out, and
+    state[slot, :W] <- out. What `causal_conv(out, taps, ..., single=True)` gives and keeps, bit for bit.
+    taps float32 [W, 2]; slots int32 [R]; state float32 [slots, >= W]; shifted like out."""
+    _dev("hidden", hidden, torch.float32)
+    _dev("weight", weight)
+    _dev("bias", bias, weight.dtype)
+    _dev("out", out, weight.dtype)
+    _dev("shifted", shifted, weight.dtype)
+    _dev("taps", taps, torch.float32)
+    _dev("slots", slots, torch.int32)
+    _rows("state", state, torch.float32)
+    rows, width = hidden.shape
+    if weight.shape != (width,) or bias.shape != (width,) or out.shape != hidden.shape or shifted.shape != hidden.shape:
+        raise KernelError("add_dyt_norm_shift: weight and bias must be [width], out and shifted must have hidden's shape")
+    if taps.shape != (width, 2) or slots.numel() != rows or state.shape[1] < width:
+        raise KernelError("add_dyt_norm_shift: taps must be [width, 2], slots [rows], state rows of at least width")
+    for name, t in (("a", a), ("b", b)):
+        if t is not None:
+            _dev(name, t, weight.dtype)
+            if t.shape != hidden.shape:
+                raise KernelError(f"add_dyt_norm_shift: {name} and hidden differ in shape")
+    _check(library("norm").qf_add_dyt_norm_shift(
+        _I(_is_bf16(weight.dtype)), _ptr(hidden), _ptr(a), _ptr(b), _ptr(weight), _ptr(bias), _F(alpha), _ptr(out), _ptr(taps),
+        _ptr(slots), _ptr(state), _LL(state.stride(0)), _ptr(shifted), _I(rows), _I(width), _stream()), "add_dyt_norm_shift")
+
+
 def residual_add_pair(hidden: torch.Tensor, a: Optional[torch.Tensor], b: Optional[torch.Tensor]) -> None:
     """hidden += (a + b): the two pending outputs of one layer, summed with each other first (float32)."""
     _dev("hidden", hidden, torch.float32)
@@ -1207,16 +1237,17 @@ def latent_norm_cache(down: torch.Tensor, q_rank: int, q_norm: Optional[torch.Te
         _I(1 if write_cache else 0), _I(n), _ptr(err), _stream()), "latent_norm_cache")
 
 
-def _grouped(x, weight, out, a_group_cols, c_group_cols, rows, plan, a_rows=None, gated=False, row_scale=None) -> None:
+def _grouped(x, weight, out, a_group_cols, c_group_cols, rows, plan, a_rows=None, gated=False, row_scale=None, clamp=None) -> None:
     groups, n, k = weight.shape
     if gated:
         n //= 2   # columns of the result
-    code = library("grouped_gemm").qf_grouped_gemm(
+    limit, alpha = (float(clamp[0]), float(clamp[1])) if clamp is not None else (0.0, 0.0)
+    code = library("grouped_gemm").qf_grouped_gemm_gate(
         _I(_is_bf16(x.dtype)), _ptr(x), _LL(x.stride(0)), _LL(a_group_cols), _ptr(weight), _LL(weight.stride(0)),
         _LL(weight.stride(1)), _ptr(out), _LL(out.stride(0)), _LL(c_group_cols), _I(rows), _I(n), _I(k), _I(groups),
         _ptr(plan.tile_group if plan else None), _ptr(plan.tile_row0 if plan else None), _ptr(plan.offsets if plan else None),
         _ptr(plan.n_tiles if plan else None), _I(plan.max_tiles if plan else 0), _I(plan.tile_rows if plan else 0),
-        _ptr(a_rows), _I(int(gated)), _ptr(row_scale), _stream())
+        _ptr(a_rows), _I(int(gated)), _ptr(row_scale), _F(limit), _F(alpha), _stream())
     if code == 1:
         raise KernelError("grouped_gemm: the plan's tiles do not fit these operands (tiles of 128 rows need bfloat16 operands "
                           "whose K and strides are multiples of 8), or the grid is too large")
@@ -1384,10 +1415,14 @@ def expert_gate_takes(x: torch.Tensor, weight: torch.Tensor, plan: MoePlan) -> b
 
 
 def expert_gate_up(x: torch.Tensor, weight: torch.Tensor, plan: MoePlan, out: torch.Tensor,
-                   row_scale: Optional[torch.Tensor] = None, gather: bool = False) -> None:
+                   row_scale: Optional[torch.Tensor] = None, gather: bool = False, clamp=None) -> None:
     """An expert's gate/up product and its gate in one kernel: out[row] = silu(s g) * (s u) with [g | u] = x[row] @
     weight[expert of the row].T, weight [E, 2 F, K] (gate rows then up rows), out [T * top, F], s = row_scale[row] (float32) or
-    1. `gather` as in `expert_linear`. bfloat16 on the tensor cores only (`expert_gate_takes`)."""
+    1. `gather` as in `expert_linear`. bfloat16 on the tensor cores only (`expert_gate_takes`).
+    clamp = (limit, alpha), limit > 0: the clamped gate instead, min(g, limit) sigmoid(alpha min(g, limit)) (clamp(u, -limit,
+    limit) + 1), on the float32 sums."""
+    if clamp is not None and not float(clamp[0]) > 0:
+        raise KernelError("expert_gate_up: the clamped gate needs a positive limit")
     _dev("x", x, torch.bfloat16)
     _dev("weight", weight, torch.bfloat16)
     _dev("out", out, torch.bfloat16)
@@ -1398,7 +1433,7 @@ def expert_gate_up(x: torch.Tensor, weight: torch.Tensor, plan: MoePlan, out: to
         raise KernelError(f"expert_gate_up: shapes {tuple(x.shape)} x {tuple(weight.shape)} -> {tuple(out.shape)} do not agree")
     if row_scale is not None:
         _dev("row_scale", row_scale, torch.float32)
-    _grouped(x, weight, out, 0, 0, plan.pairs, plan, plan.sorted_token if gather else None, True, row_scale)
+    _grouped(x, weight, out, 0, 0, plan.pairs, plan, plan.sorted_token if gather else None, True, row_scale, clamp)
 
 
 def scaled_swiglu(gate_up: torch.Tensor, row_scale: torch.Tensor, out: torch.Tensor) -> None:

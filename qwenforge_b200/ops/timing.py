@@ -19,7 +19,7 @@ TIMED = ("embed_gather", "gather_rows", "add_rms_norm", "residual_add", "linear"
          "tc_gemm", "sample", "decode_advance", "wide_gemm", "fold_project", "gather_rows_norm", "embed_positions",
          "sandwich_norm", "clamped_glu", "latent_norm_cache", "head_linear", "expert_linear", "moe_plan", "moe_gather",
          "moe_combine", "tc_gemm_grouped", "scaled_swiglu", "linear_rows", "bias_act", "softcap_", "outer_state_scan", "stabilized_gates",
-         "decay_gates", "gated_group_norm", "causal_conv_silu", "causal_conv", "add_dyt_norm", "residual_add_pair", "stream_pair",
+         "decay_gates", "gated_group_norm", "causal_conv_silu", "causal_conv", "add_dyt_norm", "add_dyt_norm_shift", "residual_add_pair", "stream_pair",
          "head_gate", "pool_cache_write")
 
 

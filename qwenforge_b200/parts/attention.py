@@ -172,6 +172,9 @@ class GqaAttention(Mixer):
             pieces += [self._padded(t("k_weight"), self.n_kv, kd), self._padded(t("v_weight"), self.n_kv, vd)]
         if self.gated:   # the gates' logits are further columns of the one product
             pieces.append(t("g_weight"))
+            rows = sum(p.shape[0] for p in pieces)
+            if rows % 8:   # zero rows up to a row pitch of whole 16 bytes: the library's products choose their kernels by it
+                pieces.append(pieces[0].new_zeros((8 - rows % 8, pieces[0].shape[1])))
         self.qkv_weight = torch.cat(pieces, dim=0).contiguous()
         if self.conv_taps > 0:   # zero taps under the padding: what is zero stays zero
             self.conv_weight = torch.cat((self._padded(t("q_conv"), self.n_heads, kd), self._padded(t("k_conv"), self.n_kv, kd),
@@ -253,7 +256,7 @@ class GqaAttention(Mixer):
         kv_site = site["kv"] if bundled else site
         inv_freq, rot_dim = self.position.fused_rotary() if self.position is not None else (None, 0)
         qkv = ops.linear_rows(x, self.qkv_weight)           # [T, q | k | v (| gates)]
-        gates = qkv[:, self.qkv_width:] if self.gated else None
+        gates = qkv[:, self.qkv_width:self.qkv_width + self.n_heads] if self.gated else None
         if self.conv_taps > 0:
             mixed = torch.empty((n, self.qkv_width), dtype=x.dtype, device=x.device)
             ops.causal_conv(qkv[:, :self.qkv_width], self.conv_weight, None, ctx.cu_q, ctx.tok_seq, ctx.slots, site["conv"].storage,

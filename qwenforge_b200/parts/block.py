@@ -120,19 +120,27 @@ class ParallelBlock(Part):
         return BundleNeed((("input", self.mixer_input.cache_need()), ("mixer", need)))
 
     def forward(self, hidden, delta, ctx, site, writes_cache):
+        bundled = self.mixer_input is not None and self.mixer_input.cache_need() is not None
+        if bundled and not writes_cache:
+            raise ValueError("parallel: a layer whose mixer input keeps a state cannot read another entry's cache")
+        # a mixer input that the norm's kernel can make on its way (single tokens): one launch for both
+        rider = None
+        if bundled and getattr(self.norm, "takes_shift", False) and hasattr(self.mixer_input, "rides_on_norm"):
+            rider = self.mixer_input.rides_on_norm(hidden.shape[0], ctx, site["input"])
+        extra = {} if rider is None else {"shift": rider}
         if isinstance(delta, PendingPair):
             if self.pair_norm:
-                h = self.norm.forward(hidden, delta.a, delta.b)
+                h = self.norm.forward(hidden, delta.a, delta.b, **extra)
             else:
                 delta.add_to(hidden)
-                h = self.norm.forward(hidden, None)
+                h = self.norm.forward(hidden, None, **extra)
         else:
-            h = self.norm.forward(hidden, delta)
+            h = self.norm.forward(hidden, delta, **extra)
         mixer_site, u = site, h
-        if self.mixer_input is not None:
-            bundled = self.mixer_input.cache_need() is not None
-            if bundled and not writes_cache:
-                raise ValueError("parallel: a layer whose mixer input keeps a state cannot read another entry's cache")
+        if rider is not None:
+            h, u = h
+            mixer_site = site["mixer"]
+        elif self.mixer_input is not None:
             u = self.mixer_input.forward(h, ctx, site["input"] if bundled else None)
             mixer_site = site["mixer"] if bundled else site
         mixed = self.mixer.forward(u, ctx, mixer_site, writes_cache)

@@ -135,10 +135,14 @@ class RoutedExperts(FeedForward):
                 y = torch.empty_like(rows)
                 ops.tc_gemm_grouped(ops.TC_PLAIN, act, self.down, plan, y, None, ctx.err)
                 return RowSum(y, plan.dest, self.top, plan.sorted_weight)
-            # otherwise the rows are read through the plan's row map; both halves in one product, then the clamped gate
-            gate_up = torch.empty((plan.pairs, 2 * self.inter), dtype=x.dtype, device=x.device)
-            ops.expert_linear(x, self.gate_up, plan, gate_up, gather=True)
-            ops.clamped_glu(gate_up, self.limit, self.alpha, act)
+            # otherwise the rows are read through the plan's row map: the clamped gate in the product's epilogue where the small
+            # tensor-core tile takes the operands, else both halves in one product and the gate behind it
+            if self.limit > 0 and ops.expert_gate_takes(x, self.gate_up, plan):
+                ops.expert_gate_up(x, self.gate_up, plan, act, None, gather=True, clamp=(self.limit, self.alpha))
+            else:
+                gate_up = torch.empty((plan.pairs, 2 * self.inter), dtype=x.dtype, device=x.device)
+                ops.expert_linear(x, self.gate_up, plan, gate_up, gather=True)
+                ops.clamped_glu(gate_up, self.limit, self.alpha, act)
             ops.expert_linear(act, self.down, plan, rows)
             return RowSum(rows, plan.dest, self.top, plan.sorted_weight)
         # A weight on the expert's input moves behind its first product (G (w h) = w (G h), and the same for U), where it

@@ -68,10 +68,18 @@ class DynamicTanh(Norm):
         self.bias = tensors[self.file_name("bias")]
         self.alpha = float(tensors[self.file_name("alpha")].float().item())
 
-    def forward(self, hidden: torch.Tensor, delta: Optional[torch.Tensor], second: Optional[torch.Tensor] = None) -> torch.Tensor:
+    takes_shift = True
+
+    def forward(self, hidden: torch.Tensor, delta: Optional[torch.Tensor], second: Optional[torch.Tensor] = None, shift=None):
+        """shift: None, or (taps [W, 2] float32, slots [R], state [slots, >= W]) in a step of one token per sequence: the
+        token shift behind this norm rides in its kernel, and the result is the pair (out, shifted)."""
         out = torch.empty(hidden.shape, dtype=self.weight.dtype, device=hidden.device)
-        ops.add_dyt_norm(hidden, delta, second, self.weight, self.bias, self.alpha, out)
-        return out
+        if shift is None:
+            ops.add_dyt_norm(hidden, delta, second, self.weight, self.bias, self.alpha, out)
+            return out
+        shifted = torch.empty_like(out)
+        ops.add_dyt_norm_shift(hidden, delta, second, self.weight, self.bias, self.alpha, out, shift[0], shift[1], shift[2], shifted)
+        return out, shifted
 
     def step_weights(self):
         return [self.weight, self.bias]

@@ -76,6 +76,13 @@ class TokenShift(Part):
     def step_weights(self):
         return [self.taps]
 
+    def rides_on_norm(self, n_rows: int, ctx, site):
+        """What a norm kernel that takes a shift needs to do this part's work itself, in a step of one token per sequence
+        (else None): the taps, the step's slots, the kept rows."""
+        if not (ctx.is_decode and n_rows == ctx.n_seqs):
+            return None
+        return self.taps, ctx.slots, site.storage
+
     def forward(self, h: torch.Tensor, ctx, site) -> torch.Tensor:
         out = torch.empty_like(h)
         ops.causal_conv(h, self.taps, None, ctx.cu_q, ctx.tok_seq, ctx.slots, site.storage, 0, out,

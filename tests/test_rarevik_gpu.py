@@ -135,6 +135,74 @@ def test_convolution_without_activation(dtype, taps, channels):
         assert max_err(states[0], states[1]) < 1e-6
 
 
+@pytest.mark.parametrize("dtype", BOTH)
+@pytest.mark.parametrize("taps,channels", [(2, 72), (3, 40), (4, 136)])
+def test_long_steps_of_the_convolution_agree_bit_for_bit_with_short_ones(dtype, taps, channels):
+    """A long step runs on the kernel that walks runs of tokens with the last inputs in registers; the same tokens in steps too
+    short for it run on the kernel of one thread per output. Sequences that begin inside a run, of one and two tokens, with a
+    state from an earlier step and without a slot."""
+    from qwenforge_b200 import ops
+    g = torch.Generator().manual_seed(taps * channels)
+    weight = rand(g, channels, taps)
+    lengths, slots = [13, 1, 2, 41, 7, 30], [2, 0, -1, 1, 3, 4]
+    before = rand(g, 5, (taps - 1) * channels)
+    per_seq = [rand(g, n, channels, dtype=dtype) for n in lengths]
+    whole, whole_state = Batch(slots, [(3, n) for n in lengths]), before.clone()
+    out = torch.empty(whole.n_tokens, channels, dtype=dtype, device=DEV)
+    ops.causal_conv(torch.cat(per_seq), weight, None, whole.cu_q, whole.tok_seq, whole.slots, whole_state, 0, out)
+    want, want_state = torch.empty_like(out), before.clone()
+    refs.causal_conv(torch.cat(per_seq), weight, None, whole.cu_q, whole.tok_seq, whole.slots, want_state, 0, want)
+    close(out, want, dtype, "conv of a long step", bf16=1e-2)
+    assert max_err(whole_state, want_state) < 1e-6
+    pieces, piece_state, begin = [], before.clone(), 0
+    for s, (n, slot) in enumerate(zip(lengths, slots)):
+        for cut in range(0, n, 9):
+            part = per_seq[s][cut:cut + 9]
+            batch = Batch([slot], [(3 + cut, part.shape[0])])
+            got = torch.empty(part.shape[0], channels, dtype=dtype, device=DEV)
+            if slot < 0 and cut > 0:     # nothing is kept without a slot: such a sequence cannot be cut
+                got = out[begin + cut:begin + cut + part.shape[0]].clone()
+            else:
+                ops.causal_conv(part, weight, None, batch.cu_q, batch.tok_seq, batch.slots, piece_state, 0, got)
+            pieces.append(got)
+        begin += n
+    assert torch.equal(torch.cat(pieces), out)
+    assert torch.equal(piece_state, whole_state)
+
+
+@pytest.mark.parametrize("dtype", BOTH)
+@pytest.mark.parametrize("width", [45, 384])
+def test_token_shift_inside_the_norm_kernel_is_the_convolution_behind_it(dtype, width):
+    from qwenforge_b200 import ops
+    g = torch.Generator().manual_seed(width + 1)
+    a, b, w, s = rand(g, 4, width, dtype=dtype), rand(g, 4, width, dtype=dtype), rand(g, width, dtype=dtype), rand(g, width, dtype=dtype)
+    frac = torch.rand(width, generator=g).to(DEV)
+    taps = torch.stack((frac, 1.0 - frac), dim=1).contiguous()
+    slots, every = ints([3, -1, 0, 5]), ints([0, 1, 2, 3, 4])
+    states = [rand(g, 6, width + 7).clone() for _ in range(2)]
+    states[1].copy_(states[0])
+    for _ in range(3):     # a few steps in a row: what one leaves the next one reads
+        hidden = rand(g, 4, width, spread=3.0)
+        twin = hidden.clone()
+        out, shifted = torch.empty(4, width, dtype=dtype, device=DEV), torch.empty(4, width, dtype=dtype, device=DEV)
+        ops.add_dyt_norm_shift(hidden, a, b, w, s, 0.7, out, taps, slots, states[0], shifted)
+        want, want_shifted = torch.empty_like(out), torch.empty_like(out)
+        ops.add_dyt_norm(twin, a, b, w, s, 0.7, want)
+        ops.causal_conv(want, taps, None, every, every[:-1], slots, states[1], 0, want_shifted, single=True)
+        assert torch.equal(hidden, twin) and torch.equal(out, want) and torch.equal(shifted, want_shifted)
+        assert torch.equal(states[0], states[1])
+        ref_hidden, ref_out, ref_shifted = twin.clone(), torch.empty_like(out), torch.empty_like(out)
+    state = rand(g, 6, width)
+    ref_state = state.clone()
+    hidden = rand(g, 4, width, spread=3.0)
+    ref_hidden = hidden.clone()
+    ops.add_dyt_norm_shift(hidden, a, None, w, s, 1.3, out, taps, slots, state, shifted)
+    refs.add_dyt_norm_shift(ref_hidden, a, None, w, s, 1.3, ref_out, taps, slots, ref_state, ref_shifted)
+    close(out, ref_out, dtype, "dyt", bf16=1e-2)
+    close(shifted, ref_shifted, dtype, "shifted", bf16=2e-2)
+    close(state, ref_state, dtype, "kept", bf16=1e-2)
+
+
 def two_caches(kv_heads, dim, dtype, pool=0, window=0):
     from qwenforge_b200.cache import BundleNeed, KvNeed, SequenceCache
     need = KvNeed(kv_heads, dim, window, pool=pool)
@@ -317,6 +385,29 @@ def test_clamped_gate_in_the_grouped_tensor_core_product():
         refs.tc_gemm_grouped(1, rows, weight, Routing, want, clamp=(limit, 1.702))
         assert int(err) == 0
         close(out, want, torch.bfloat16, f"limit {limit}", bf16=2e-2)
+
+
+def test_clamped_gate_in_the_small_grouped_product():
+    """Short steps: the experts' first product through the plan's row map, tiles of 64 rows, the clamped gate on its float32
+    sums; experts without a row, rows that do not fill a tile, an expert size that is no multiple of the tile's columns."""
+    from qwenforge_b200 import ops
+    g = torch.Generator().manual_seed(6)
+    for tokens, experts, top, width, inter in ((8, 8, 2, 128, 40), (70, 3, 3, 64, 112)):
+        x, router = rand(g, tokens, width, dtype=torch.bfloat16), rand(g, experts, width, dtype=torch.bfloat16, spread=0.3)
+        weight = rand(g, experts, 2 * inter, width, dtype=torch.bfloat16, spread=0.2)
+        plan = ops.moe_plan(ops.linear(x, router, out_dtype=torch.float32), top, True, True, 64)
+        assert ops.expert_gate_takes(x, weight, plan)
+        rows = torch.empty(tokens * top, width, dtype=torch.bfloat16, device=DEV)
+        ops.moe_gather(x, plan, rows, False)
+        experts_of = torch.empty(tokens * top, dtype=torch.long, device=DEV)
+        experts_of[plan.dest.long()] = plan.pair_expert.long()
+        class Routing:
+            row_expert = experts_of
+        for limit in (0.5, 50.0):
+            out, want = (torch.empty(tokens * top, inter, dtype=torch.bfloat16, device=DEV) for _ in range(2))
+            ops.expert_gate_up(x, weight, plan, out, None, gather=True, clamp=(limit, 1.702))
+            refs.tc_gemm_grouped(1, rows, weight, Routing, want, clamp=(limit, 1.702))
+            close(out, want, torch.bfloat16, f"limit {limit}", bf16=2e-2)
 
 
 # ------------------------------------------------------------------------------------------------ the model
