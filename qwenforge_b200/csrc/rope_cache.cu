@@ -86,12 +86,25 @@ __global__ void rope_cache_kernel(const T* __restrict__ qkv, const T* __restrict
 
 // The same for bfloat16 with rows that 16-byte accesses can address (head size, rotated part and row stride
 // multiples of 8 elements when halved): a block takes RC_TOKENS tokens, a thread eight components at a time.
+// OPTS: the pairs of the rotation may be neighbours (`interleaved`: 2j with 2j + 1; a thread then takes sixteen consecutive
+// components), and q and k heads may be divided by their root mean square BEFORE the rotation, times a weight per component
+// (`eps` >= 0; `q_norm`, `k_norm` or null). The norm wants the whole head rotated (rot_dim == head size) and a number of
+// threads per head (rot_dim / 16) that is a power of two: the head's threads are then neighbours in one warp and add their
+// sums of squares by shuffles, the same sum in every one of them.
+struct RopeVecOpts {
+    int interleaved;
+    float eps;              // < 0: no norm
+    const bf16* q_norm;
+    const bf16* k_norm;
+};
+
 #define RC_TOKENS 4
+template <bool OPTS>
 __global__ void __launch_bounds__(256)
 rope_cache_vec_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ bias, int qkv_stride, const int* __restrict__ tok_seq,
                       const int* __restrict__ tok_pos, const int* __restrict__ slots, const float* __restrict__ inv_freq,
                       int rot_dim, int n_heads, bf16* __restrict__ q_out, KvSite<bf16> site, int write_cache, int n_tokens,
-                      int* err) {
+                      int* err, RopeVecOpts opts) {
     grid_chain_entry();
     const int D = site.head_dim, KVH = site.kv_heads;
     const int half = rot_dim / 2, pass = D - rot_dim;
@@ -150,24 +163,59 @@ rope_cache_vec_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ bia
         const bf16* row = qkv + (size_t)t * qkv_stride;
         const long long cache_off = page_s[k];
         if (item < rot_groups) {
-            const int head = item / (half / 8), j = (item % (half / 8)) * 8;
+            const int per_head = half / 8, head = item / per_head, j = (item % per_head) * 8;
             const bool is_q = head < n_heads;
             const int src = is_q ? head * D : q_width + (head - n_heads) * D;
+            const bool neighbours = OPTS && opts.interleaved;
+            const int ja = neighbours ? 2 * j : j, jb = neighbours ? 2 * j + 8 : j + half;   // the thread's two runs of eight
             float x1[8], x2[8], o1[8], o2[8];
-            load8(row + src + j, bias ? bias + src + j : nullptr, x1);
-            load8(row + src + j + half, bias ? bias + src + j + half : nullptr, x2);
+            load8(row + src + ja, bias ? bias + src + ja : nullptr, x1);
+            load8(row + src + jb, bias ? bias + src + jb : nullptr, x2);
+            if (OPTS && opts.eps >= 0.f) {
+                float ss = 0.f;
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                const float s = sin_s[k][j + e], c = cos_s[k][j + e];
-                o1[e] = x1[e] * c - x2[e] * s;
-                o2[e] = x2[e] * c + x1[e] * s;
+                for (int e = 0; e < 8; ++e) ss = fmaf(x1[e], x1[e], ss);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) ss = fmaf(x2[e], x2[e], ss);
+                const int lane = threadIdx.x & 31;
+                const unsigned group = per_head >= 32 ? 0xffffffffu : ((1u << per_head) - 1u) << (lane & ~(per_head - 1));
+                for (int off = 1; off < per_head; off <<= 1) ss += __shfl_xor_sync(group, ss, off);
+                const float before = 1.f / sqrtf(ss / (float)D + opts.eps);
+                const bf16* gain = is_q ? opts.q_norm : opts.k_norm;
+                float g1[8], g2[8];
+                if (gain) {
+                    load8(gain + ja, nullptr, g1);
+                    load8(gain + jb, nullptr, g2);
+                }
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    x1[e] = gain ? x1[e] * before * g1[e] : x1[e] * before;
+                    x2[e] = gain ? x2[e] * before * g2[e] : x2[e] * before;
+                }
+            }
+            if (neighbours) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float s1 = sin_s[k][j + e], c1 = cos_s[k][j + e], s2 = sin_s[k][j + 4 + e], c2 = cos_s[k][j + 4 + e];
+                    o1[2 * e] = x1[2 * e] * c1 - x1[2 * e + 1] * s1;
+                    o1[2 * e + 1] = x1[2 * e + 1] * c1 + x1[2 * e] * s1;
+                    o2[2 * e] = x2[2 * e] * c2 - x2[2 * e + 1] * s2;
+                    o2[2 * e + 1] = x2[2 * e + 1] * c2 + x2[2 * e] * s2;
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float s = sin_s[k][j + e], c = cos_s[k][j + e];
+                    o1[e] = x1[e] * c - x2[e] * s;
+                    o2[e] = x2[e] * c + x1[e] * s;
+                }
             }
             bf16* dst = nullptr;
             if (is_q) dst = q_out + (size_t)t * q_width + head * D;
             else if (cache_off >= 0) dst = site.base + cache_off + (long long)(head - n_heads) * QF_PAGE * D;
             if (dst) {
-                store8(dst + j, o1);
-                store8(dst + j + half, o2);
+                store8(dst + ja, o1);
+                store8(dst + jb, o2);
             }
         } else {
             int rest = item - rot_groups;
@@ -200,9 +248,10 @@ static int launch(const void* qkv, const void* bias, int qkv_stride, const int* 
     if (!inv_freq) rot_dim = 0;
     if (sizeof(T) == 2 && head_dim % 16 == 0 && rot_dim % 16 == 0 && qkv_stride % 8 == 0 && head_dim <= 256 &&
         ((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)base | (uintptr_t)bias) % 16 == 0 && page_elems % 8 == 0) {
-        return (int)launch_pdl(rope_cache_vec_kernel, dim3((n_tokens + RC_TOKENS - 1) / RC_TOKENS), dim3(256), 0, stream,
+        return (int)launch_pdl(rope_cache_vec_kernel<false>, dim3((n_tokens + RC_TOKENS - 1) / RC_TOKENS), dim3(256), 0, stream,
             (const bf16*)qkv, (const bf16*)bias, qkv_stride, tok_seq, tok_pos, slots, inv_freq, rot_dim, n_heads, (bf16*)q_out,
-            KvSite<bf16>{(bf16*)base, table, page_elems, table_stride, kv_heads, head_dim}, write_cache, n_tokens, err);
+            KvSite<bf16>{(bf16*)base, table, page_elems, table_stride, kv_heads, head_dim}, write_cache, n_tokens, err,
+            RopeVecOpts{0, -1.f, nullptr, nullptr});
     }
     return (int)launch_pdl(rope_cache_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (const T*)qkv, (const T*)bias, qkv_stride, tok_seq, tok_pos, slots, inv_freq,
                                                        rot_dim, n_heads, (T*)q_out, site, write_cache, err);
@@ -242,6 +291,7 @@ rope_norm_cache_kernel(const T* __restrict__ qkv, const T* __restrict__ bias, in
     const int D = site.head_dim, KVH = has_kv ? site.kv_heads : 0;
     const int heads_per_token = n_heads + 2 * KVH;
     const int lane = threadIdx.x & 31;
+    const int half = rot_dim / 2;
     const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (item >= (long long)n_tokens * heads_per_token) return;
     const int t = (int)(item / heads_per_token), head = (int)(item % heads_per_token);
@@ -257,7 +307,6 @@ rope_norm_cache_kernel(const T* __restrict__ qkv, const T* __restrict__ bias, in
     }
     if (!dst) return;
     const T* row = qkv + (size_t)t * qkv_stride + src;
-    const int half = rot_dim / 2;
     const bool normed = !is_v && eps >= 0.f;
     const T* gain = is_q ? q_norm : k_norm;   // the norm's weight, where it has one
     auto raw = [&](int d) { return Num<T>::to_f(row[d]) + (bias ? Num<T>::to_f(bias[src + d]) : 0.f); };
@@ -316,6 +365,18 @@ QF_EXPORT int qf_rope_norm_cache_write_ex(int is_bf16, const void* qkv, const vo
     if (!inv_freq) rot_dim = 0;
     if (rot_dim < 0 || rot_dim > head_dim || (rot_dim & 1) || head_dim > 32 * RN_MAX_PER_LANE || norm_dim <= 0 || norm_dim > head_dim)
         return (int)cudaErrorInvalidValue;
+    // long steps of bfloat16 rows that 16-byte accesses can address: eight components per thread, the angles once per token
+    const int per_head = rot_dim / 16;
+    const bool norm_fits = eps < 0.f || (norm_first && norm_dim == head_dim && rot_dim == head_dim && per_head >= 1 && per_head <= 32 &&
+                                         (per_head & (per_head - 1)) == 0);
+    if (is_bf16 && has_kv && n_tokens >= 4 * RC_TOKENS && norm_fits && head_dim % 16 == 0 && rot_dim % 16 == 0 && qkv_stride % 8 == 0 &&
+        head_dim <= 256 && page_elems % 8 == 0 &&
+        ((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)base | (uintptr_t)bias | (uintptr_t)q_norm | (uintptr_t)k_norm) % 16 == 0) {
+        return (int)launch_pdl(rope_cache_vec_kernel<true>, dim3((n_tokens + RC_TOKENS - 1) / RC_TOKENS), dim3(256), 0, stream,
+            (const bf16*)qkv, (const bf16*)bias, qkv_stride, tok_seq, tok_pos, slots, inv_freq, rot_dim, n_heads, (bf16*)q_out,
+            KvSite<bf16>{(bf16*)base, table, page_elems, table_stride, kv_heads, head_dim}, write_cache, n_tokens, err,
+            RopeVecOpts{interleaved, eps, (const bf16*)q_norm, (const bf16*)k_norm});
+    }
     const long long items = (long long)n_tokens * (n_heads + (has_kv ? 2 * kv_heads : 0));
     const dim3 grid((unsigned)((items + 7) / 8)), block(256);
     if (is_bf16)

@@ -32,6 +32,8 @@ struct SkinnyArgs {
     long long page_elems;
     int table_stride;
     int* err;
+    // SWIGLU with gate_limit > 0: the clamped gate min(g, limit) sigmoid(gate_alpha min(g, limit)) (clamp(u, -limit, limit) + 1)
+    float gate_limit, gate_alpha;
 };
 
 template <int EPI> __device__ __forceinline__ void tile_rows(const SkinnyArgs& a, int tile, int g, int& ra, int& rb) {
@@ -124,8 +126,15 @@ __device__ __forceinline__ void skinny_epilogue(const SkinnyArgs& a, int tile, i
                 if (ra >= 0) h[ra] = pre.res[nt][e] + va;
                 if (rb >= 0) h[rb] = pre.res[nt][2 + e] + vb;
             } else if (EPI == EPI_SWIGLU) {
-                if (ra >= 0)
-                    reinterpret_cast<bf16*>(a.out)[(size_t)m * a.ldo + ra] = __float2bfloat16_rn(va / (1.0f + expf(-va)) * vb);
+                if (ra >= 0) {
+                    float gate = va, up = vb, slope = 1.0f;
+                    if (a.gate_limit > 0.f) {
+                        gate = fminf(va, a.gate_limit);
+                        up = fminf(fmaxf(vb, -a.gate_limit), a.gate_limit) + 1.0f;
+                        slope = a.gate_alpha;
+                    }
+                    reinterpret_cast<bf16*>(a.out)[(size_t)m * a.ldo + ra] = __float2bfloat16_rn(gate / (1.0f + expf(-slope * gate)) * up);
+                }
             } else if (ra >= 0) {  // EPI_QKV
                 const int D = a.head_dim, head = ra / D, j = ra % D;  // rb is component j + D/2 of the same head
                 float oa = va, ob = vb;

@@ -6,7 +6,7 @@ from .kernels import (TC_PLAIN, TC_SWIGLU, tc_gemm, tc_gemm_takes, tc_gemm_is_pe
                       ERR_POSITION_RANGE, GENERIC_MAX_HEAD_DIM, bias_act, softcap_, stabilized_gates, decay_gates, outer_state_scan,
                       gated_group_norm, causal_conv_silu, OUTER_STATE_MAX_DIM, CONV_MAX_TAPS, ACTIVATIONS,
                       add_dyt_norm, add_dyt_norm_shift, residual_add_pair, stream_pair, head_gate, pool_cache_write, causal_conv)
-from .linear import linear, linear_rows, own_tensor_core_products, use_own_tensor_core_products
+from .linear import linear, linear_rows, gated_rows, own_tensor_core_products, use_own_tensor_core_products
 
 __all__ = [
     "add_dyt_norm", "add_dyt_norm_shift", "residual_add_pair", "stream_pair", "head_gate", "pool_cache_write", "causal_conv",
@@ -14,7 +14,7 @@ __all__ = [
     "OUTER_STATE_MAX_DIM", "CONV_MAX_TAPS", "ACTIVATIONS",
     "embed_positions", "sandwich_norm", "clamped_glu", "latent_norm_cache", "head_linear", "MoePlan", "moe_plan", "moe_gather",
     "moe_combine", "expert_linear", "ERR_POSITION_RANGE", "GENERIC_MAX_HEAD_DIM", "scaled_swiglu", "moe_tile_rows",
-    "MOE_FUSED_ROUTER_MAX", "linear_rows", "tc_gemm_grouped", "tc_gemm_grouped_takes", "expert_gate_up", "expert_gate_takes",
+    "MOE_FUSED_ROUTER_MAX", "linear_rows", "gated_rows", "tc_gemm_grouped", "tc_gemm_grouped_takes", "expert_gate_up", "expert_gate_takes",
     "ERR_NO_PAGE", "ERR_ROW_RANGE", "ERR_TOKEN_RANGE", "KernelError", "KvSiteArgs", "add_rms_norm",
     "attention_generic", "describe_error_word", "embed_gather", "gather_rows", "gather_rows_norm", "gemm_f32", "rope_cache_write",
     "sample", "swiglu", "linear", "own_tensor_core_products", "use_own_tensor_core_products", "require_cuda", "FAST_ATTENTION_HEAD_DIMS", "GENERIC_DECODE_CHUNK", "DecodeScratch",

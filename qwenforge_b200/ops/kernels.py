@@ -646,7 +646,7 @@ class _SkinnyArgs(ctypes.Structure):
         ("out", _P), ("ldo", _I), ("out_f32", _I), ("residual", _P), ("inter", _I),
         ("n_heads", _I), ("kv_heads", _I), ("head_dim", _I), ("rot_dim", _I), ("write_cache", _I),
         ("inv_freq", _P), ("tok_pos", _P), ("tok_seq", _P), ("slots", _P), ("q_out", _P), ("kv_base", _P),
-        ("table", _P), ("page_elems", _LL), ("table_stride", _I), ("err", _P),
+        ("table", _P), ("page_elems", _LL), ("table_stride", _I), ("err", _P), ("gate_limit", _F), ("gate_alpha", _F),
     ]
 
 
@@ -702,8 +702,9 @@ def _skinny_args(epilogue: int, weight: torch.Tensor, *, x: Optional[torch.Tenso
                  hidden: Optional[torch.Tensor] = None, norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0,
                  bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
                  residual: Optional[torch.Tensor] = None, qkv: Optional[dict] = None,
-                 err: Optional[torch.Tensor] = None):
-    """Checks one fused product's tensors and fills the kernels' argument block; returns (block, norm flag)."""
+                 err: Optional[torch.Tensor] = None, clamp=None):
+    """Checks one fused product's tensors and fills the kernels' argument block; returns (block, norm flag).
+    clamp = (limit, alpha) with EPI_SWIGLU: the clamped gate in the silu gate's place (see `clamped_glu`)."""
     _dev("weight", weight, torch.bfloat16, contiguous=False)
     a = _SkinnyArgs()
     a.w, a.n, a.k, a.ldw = weight.data_ptr(), weight.shape[0], weight.shape[1], weight.stride(0)
@@ -738,6 +739,10 @@ def _skinny_args(epilogue: int, weight: torch.Tensor, *, x: Optional[torch.Tenso
         if out.shape != (a.m, a.inter):
             raise KernelError("skinny_gemm: out must be [m, N / 2] bf16")
         a.out, a.ldo = out.data_ptr(), out.stride(0)
+        if clamp is not None:
+            if not float(clamp[0]) > 0:
+                raise KernelError("skinny_gemm: the clamped gate needs a positive limit")
+            a.gate_limit, a.gate_alpha = float(clamp[0]), float(clamp[1])
     elif epilogue == EPI_QKV:
         site = qkv["site"]
         _dev("q_out", qkv["q_out"], torch.bfloat16)

@@ -81,3 +81,17 @@ def linear_rows(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch
         kernels.skinny_gemm(kernels.EPI_PLAIN, weight, x=x, out=out)
         return out
     return linear(x, weight, None, out_dtype=out_dtype)
+
+
+def gated_rows(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, clamp=None) -> bool:
+    """The fused [gate | up] product of a step of few rows with its gate in the product's epilogue, where this library's weight
+    streamer takes the shape and is the faster way: out = silu(g) * u, or with clamp = (limit, alpha) the clamped gate of
+    `clamped_glu`, on the float32 sums. Returns False, having done nothing, where the caller is to run the product and the gate
+    as two kernels."""
+    m = x.shape[0]
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and m <= kernels.SKINNY_MAX_ROWS
+            and x.stride(1) == 1 and (clamp is None or float(clamp[0]) > 0)
+            and kernels.skinny_gemm_takes(m, weight, kernels.EPI_SWIGLU, False, ldx=x.stride(0)) and kernels.skinny_gemm_pays(m, weight)):
+        return False
+    kernels.skinny_gemm(kernels.EPI_SWIGLU, weight, x=x, out=out, clamp=clamp)
+    return True

@@ -102,7 +102,9 @@ class RoutedExperts(FeedForward):
         if self.shared is not None:   # the expert that every token gets rides on the kernel that sums the chosen ones
             act = torch.empty((x.shape[0], int(self.shared["size"])), dtype=x.dtype, device=x.device)
             if self.gate == "clamped":
-                ops.clamped_glu(ops.linear_rows(x, self.shared_gate_up), float(self.shared.get("limit") or self.limit), self.alpha, act)
+                limit = float(self.shared.get("limit") or self.limit)
+                if not ops.gated_rows(x, self.shared_gate_up, act, clamp=(limit, self.alpha)):   # few rows: the gate in the product
+                    ops.clamped_glu(ops.linear_rows(x, self.shared_gate_up), limit, self.alpha, act)
             else:
                 ops.swiglu(ops.linear_rows(x, self.shared_gate_up), act)
             extra = ops.linear_rows(act, self.shared_down)

@@ -442,6 +442,10 @@ def add_dyt_norm_shift(hidden, a, b, weight, bias, alpha, out, taps, slots, stat
     causal_conv(out, taps, None, every, every[:-1], slots, state, 0, shifted, single=True)
 
 
+def gated_rows(x, weight, out, clamp=None):
+    return False     # the product and the gate as two steps
+
+
 def residual_add_pair(hidden, a, b):
     if a is not None or b is not None:
         hidden += ((0 if a is None else _f(a)) + (0 if b is None else _f(b))).to(hidden.dtype)
@@ -471,7 +475,7 @@ def pool_cache_write(cu_q, tok_pos, slots, site, blocks, pool, max_q_len, err):
             blocks.storage[page, 1, :, block % PAGE, :] = v.mean(1).to(blocks.storage.dtype)
 
 
-ALL = dict(causal_conv=causal_conv, add_dyt_norm=add_dyt_norm, add_dyt_norm_shift=add_dyt_norm_shift, residual_add_pair=residual_add_pair, stream_pair=stream_pair,
+ALL = dict(gated_rows=gated_rows, causal_conv=causal_conv, add_dyt_norm=add_dyt_norm, add_dyt_norm_shift=add_dyt_norm_shift, residual_add_pair=residual_add_pair, stream_pair=stream_pair,
            head_gate=head_gate, pool_cache_write=pool_cache_write, bias_act=bias_act, softcap_=softcap_, stabilized_gates=stabilized_gates, decay_gates=decay_gates,
            outer_state_scan=outer_state_scan, gated_group_norm=gated_group_norm, causal_conv_silu=causal_conv_silu,
            expert_gate_takes=expert_gate_takes, linear_rows=linear_rows, moe_tile_rows=moe_tile_rows, scaled_swiglu=scaled_swiglu, embed_positions=embed_positions, sandwich_norm=sandwich_norm, clamped_glu=clamped_glu, latent_norm_cache=latent_norm_cache,

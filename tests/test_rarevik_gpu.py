@@ -214,7 +214,10 @@ def two_caches(kv_heads, dim, dtype, pool=0, window=0):
 @pytest.mark.parametrize("dtype", BOTH)
 @pytest.mark.parametrize("heads,kv_heads,dim,norm_dim,rot,interleaved,first", [
     (4, 2, 14, 10, 6, False, True), (3, 3, 64, 64, 64, True, False), (2, 1, 40, 40, 0, False, True), (5, 1, 96, 96, 48, True, False),
-    (2, 2, 128, 96, 96, False, True), (2, 1, 20, 20, 20, True, True)])
+    (2, 2, 128, 96, 96, False, True), (2, 1, 20, 20, 20, True, True),
+    # whole heads normed and rotated, in sizes that the kernel of eight components per thread takes in long bfloat16 steps
+    (14, 2, 64, 64, 64, False, True), (3, 1, 128, 128, 128, False, True), (2, 2, 32, 32, 32, True, True), (5, 5, 16, 16, 16, False, True),
+    (4, 2, 256, 256, 256, False, True)])
 def test_norm_before_the_rotation_and_neighbours_paired(dtype, heads, kv_heads, dim, norm_dim, rot, interleaved, first):
     """The weighted RMS norm of q and k before the rotation over a head's own components (the rest are padding and stay zero),
     the rotation of halves or of neighbours, queries out and keys and values into the pages, from rows that are wider."""
@@ -408,6 +411,29 @@ def test_clamped_gate_in_the_small_grouped_product():
             ops.expert_gate_up(x, weight, plan, out, None, gather=True, clamp=(limit, 1.702))
             refs.tc_gemm_grouped(1, rows, weight, Routing, want, clamp=(limit, 1.702))
             close(out, want, torch.bfloat16, f"limit {limit}", bf16=2e-2)
+
+
+def test_clamped_gate_in_the_product_of_few_rows():
+    """The shared expert's first product in steps of few rows: the weight streamer with the clamped gate on its float32 sums,
+    against the product and the gate as two steps."""
+    from qwenforge_b200 import ops
+    g = torch.Generator().manual_seed(8)
+    ran = 0
+    for rows, width, inter in ((1, 256, 96), (8, 896, 608), (16, 512, 1024)):
+        x = rand(g, rows, width, dtype=torch.bfloat16)
+        weight = rand(g, 2 * inter, width, dtype=torch.bfloat16, spread=0.1)
+        for limit in (0.7, 40.0):
+            out, want = (torch.zeros(rows, inter, dtype=torch.bfloat16, device=DEV) for _ in range(2))
+            if not ops.gated_rows(x, weight, out, clamp=(limit, 1.702)):
+                continue
+            ran += 1
+            refs.clamped_glu(refs.linear(x, weight, out_dtype=torch.float32), limit, 1.702, want)
+            close(out, want, torch.bfloat16, f"rows {rows}, limit {limit}", bf16=2e-2)
+        plain_out, plain_want = torch.zeros_like(out), torch.zeros_like(out)
+        if ops.gated_rows(x, weight, plain_out):
+            refs.swiglu(refs.linear(x, weight, out_dtype=torch.float32), plain_want)
+            close(plain_out, plain_want, torch.bfloat16, f"rows {rows}, silu", bf16=2e-2)
+    assert ran > 0
 
 
 # ------------------------------------------------------------------------------------------------ the model
