@@ -437,11 +437,12 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ x, int x_stride, c
     out[(size_t)t * channels + c] = Num<T>::from_f(plain ? z : z / (1.f + expf(-z)));
 }
 
-// The same convolution for long steps: a thread takes 16 bytes of channels and a run of CONV_RUN consecutive tokens, keeps
+// The same convolution for long steps: a thread takes 16 bytes of channels and a run of CONV_RUN(TAPS) consecutive tokens, keeps
 // the last TAPS - 1 inputs in registers as it walks down the run, and fetches them afresh (from the state, or zeros) where a
 // sequence begins inside the run. Every output is the same chain of fused multiply-adds, oldest input first, as in the
 // kernel of one thread per (token, channel): the two agree bit for bit.
-#define CONV_RUN 8
+// tokens of a run: the more taps, the more a longer run saves (taps - 1 inputs are fetched again at the start of every run)
+#define CONV_RUN(TAPS) ((TAPS) >= 4 ? 8 : 4)
 
 template <typename T, int TAPS>
 __global__ void __launch_bounds__(128)
@@ -454,9 +455,10 @@ causal_conv_run_kernel(const T* __restrict__ x, int x_stride, const float* __res
     grid_chain_entry();
     const int groups = channels / V;
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const int n_runs = (n_tokens + CONV_RUN - 1) / CONV_RUN;
+    constexpr int RUN = CONV_RUN(TAPS);
+    const int n_runs = (n_tokens + RUN - 1) / RUN;
     if (i >= (long long)n_runs * groups) return;
-    const int t0 = (int)(i / groups) * CONV_RUN, c0 = (int)(i % groups) * V;
+    const int t0 = (int)(i / groups) * RUN, c0 = (int)(i % groups) * V;
     float w[V][TAPS], b[V], hist[H][V];
 #pragma unroll
     for (int v = 0; v < V; ++v) {
@@ -465,7 +467,7 @@ causal_conv_run_kernel(const T* __restrict__ x, int x_stride, const float* __res
         for (int j = 0; j < TAPS; ++j) w[v][j] = weight[(size_t)(c0 + v) * TAPS + j];
     }
 #pragma unroll
-    for (int k = 0; k < CONV_RUN; ++k) {
+    for (int k = 0; k < RUN; ++k) {
         const int t = t0 + k;
         if (t >= n_tokens) break;
         const int seq = tok_seq[t], at = t - cu_q[seq];
@@ -530,11 +532,12 @@ static int launch_conv(const void* x, int x_stride, const float* weight, const f
                        int n_tokens, int channels, void* out, int plain, int single, cudaStream_t stream) {
     const long long total = (long long)n_tokens * channels;
     constexpr int V = 16 / (int)sizeof(T);
-    const bool runs = !single && n_tokens >= 4 * CONV_RUN && (taps == 2 || taps == 3 || taps == 4) && channels % V == 0 &&
+    const bool runs = !single && n_tokens >= 32 && (taps == 2 || taps == 3 || taps == 4) && channels % V == 0 &&
                       x_stride % V == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0;
     cudaError_t e;
     if (runs) {
-        const long long items = (long long)((n_tokens + CONV_RUN - 1) / CONV_RUN) * (channels / V);
+        const int run = CONV_RUN(taps);
+        const long long items = (long long)((n_tokens + run - 1) / run) * (channels / V);
         const dim3 grid((unsigned)((items + 127) / 128)), block(128);
 #define QF_CONV_RUN(TAPS) launch_pdl(causal_conv_run_kernel<T, TAPS>, grid, block, 0, stream, (const T*)x, x_stride, weight, bias, \
                                      cu_q, tok_seq, slots, (const float*)state, slot_stride, offset, n_tokens, channels, (T*)out, plain)

@@ -407,7 +407,7 @@ QF_EXPORT int qf_rope_norm_cache_write(int is_bf16, const void* qkv, const void*
 // at position p completes the blocks floor(p / pool) .. floor((p + q) / pool) - 1. The block's positions are dealt to
 // POOL_PARTS groups of threads in turn (position j to group j % POOL_PARTS, each summing its own in rising order), and the
 // groups' sums are added in the groups' order: one fixed order of additions for a block, whatever the step that completes it.
-#define POOL_PARTS 4
+#define POOL_PARTS 16
 
 template <typename T>
 __global__ void __launch_bounds__(POOL_PARTS * 64)
