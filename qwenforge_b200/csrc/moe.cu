@@ -81,16 +81,30 @@ moe_plan_kernel(const float* logits, int n_tokens, int n_experts, int top, int s
                     // eight elements per load, and no load waits for a sum: a lane's loads are all on their way at once
                     const uint4* xv = reinterpret_cast<const uint4*>(xr);
                     const uint4* rv = reinterpret_cast<const uint4*>(rr);
-#pragma unroll 4
-                    for (int c = lane; c < width / 8; c += 32) {
-                        const uint4 a = xv[c], b = rv[c];
-                        const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
-                        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
+                    // four steps of a lane at a time, all their loads asked for before the first product (zeros beyond the
+                    // row's end add nothing): the sums run in the same order as one step after the other
+                    for (int c0 = lane; c0 < width / 8; c0 += 4 * 32) {
+                        uint4 a[4], b[4];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const float2 af = __bfloat1622float2(a2[j]), bf = __bfloat1622float2(b2[j]);
-                            sum = fmaf(af.x, bf.x, sum);
-                            sum = fmaf(af.y, bf.y, sum);
+                        for (int u = 0; u < 4; ++u) {
+                            const int c = c0 + 32 * u;
+                            a[u] = b[u] = make_uint4(0u, 0u, 0u, 0u);
+                            if (c < width / 8) {
+                                a[u] = xv[c];
+                                b[u] = rv[c];
+                            }
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            if (c0 + 32 * u >= width / 8) break;
+                            const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a[u]);
+                            const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b[u]);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const float2 af = __bfloat1622float2(a2[j]), bf = __bfloat1622float2(b2[j]);
+                                sum = fmaf(af.x, bf.x, sum);
+                                sum = fmaf(af.y, bf.y, sum);
+                            }
                         }
                     }
                 } else {
@@ -102,9 +116,10 @@ moe_plan_kernel(const float* logits, int n_tokens, int n_experts, int top, int s
                 for (int c = lane; c < width; c += 32) sum = fmaf(xr[c], rr[c], sum);
             }
             sum = warp_sum(sum);
-            if (lane == 0) logits_out[i] = sum;
+            if (lane == 0) logits_out[i] = bias ? sum + bias[e] : sum;   // the bias once, here: the choice reads shared memory only
         }
         logits = logits_out;
+        bias = nullptr;
     }
     __syncthreads();
     // pass 1: choose, and take a rank among the expert's rows
