@@ -488,10 +488,13 @@ def test_the_residual_stream_after_every_layer_run(tmp_path):
 
 
 @pytest.mark.parametrize("dtype", BOTH)
-def test_unequal_batches_in_slots_used_before(dtype, tmp_path):
+@pytest.mark.parametrize("name", ["odd", "fast"])
+def test_unequal_batches_in_slots_used_before(dtype, name, tmp_path):
     """Requests of unequal lengths start together, are decoded together and end one by one; the second round runs in slots,
-    pages and state rows that the first has used. Each request's logits equal those of the plain implementation alone."""
-    cfg = RAR_ODD
+    pages and state rows that the first has used. Each request's logits equal those of the plain implementation alone.
+    (Odd sizes run on the kernels of one element per thread, the other configuration on those of 16 bytes per thread, where
+    a sequence may begin in the middle of a thread's run of tokens.)"""
+    cfg = CONFIGS[name]
     model, weights, _ = build(cfg, tmp_path, dtype, seed=2)
     cache = model.new_cache(64 * 10, 3)
     seqs = [random_tokens(cfg["vocab"], n, 30 + n) for n in (150, 3, 66, 1, 91)]
