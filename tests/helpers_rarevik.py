@@ -75,6 +75,16 @@ RAR_WIDE = config(150, 72, 1e-5, [
     layer(pooled(6, 2, 128, 96, 70, 16, 3, 128, 100000.0, 0.1), None),
 ], loop=(1, 3, 1))
 
+# larger sizes for long prompts: steps of more than a thousand tokens (the routing plan of long steps, windows over many pages,
+# twenty experts of which four are chosen), three passes over the middle layers, heads padded from 80 and 48 to 80
+RAR_LONG = config(1000, 320, 1e-6, [
+    layer(gated(10, 2, 64, 64, 300, 64, 300000.0, None, (8.0, 1.0, 4.0, 1024)), dense(640)),
+    layer(pooled(10, 2, 80, 48, 100, 32, 4, 80, 150000.0), moe(12, 3, 96, 1.25, (160, 2.0))),
+    layer(pooled(5, 5, 64, 64, 130, 16, 2, 64, 10000.0), moe(12, 3, 96, 1.25, (160, 2.0))),
+    layer(gated(8, 4, 128, 128, 520, 128, 300000.0), moe(20, 4, 48, 7.0)),
+    layer(gated(10, 2, 64, 64, 300, 32, 1000.0), None),
+], loop=(1, 4, 3))
+
 CONFIGS = {"odd": RAR_ODD, "fast": RAR_FAST, "ones": RAR_ONES, "wide": RAR_WIDE}
 
 

@@ -14,7 +14,7 @@ import torch
 from tests import kernel_refs as refs
 from tests import plain_rarevik as plain
 from tests.helpers import max_err, random_tokens
-from tests.helpers_rarevik import CONFIGS, RAR_FAST, RAR_ODD, RAR_ONES, config, dense, gated, layer, make_model_dir, moe, pooled
+from tests.helpers_rarevik import CONFIGS, RAR_FAST, RAR_LONG, RAR_ODD, RAR_ONES, config, dense, gated, layer, make_model_dir, moe, pooled
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -469,6 +469,20 @@ def test_whole_prompts_decoding_and_portions_agree_with_the_plain_implementation
     want = plain.forward_logits(cfg, weights, tokens)
     for cuts in ([300], [260], [2, 61, 2, 130, 65, 3, 2], [129, 128]):
         logits_close(run(model, cache, tokens, cuts), want, dtype, f"{name} cuts {cuts[:3]}")
+    assert all(g.pages.n_free == g.pages.n_pages for g in cache.kv_groups)
+
+
+@pytest.mark.parametrize("dtype", BOTH)
+def test_long_prompts_at_larger_sizes(dtype, tmp_path):
+    """Steps of more than a thousand tokens: whole, with the last tokens decoded, and cut where the later portions reach back
+    over many pages."""
+    cfg, n = RAR_LONG, 1400
+    model, weights, _ = build(cfg, tmp_path, dtype, seed=11)
+    cache = model.new_cache(64 * 40, 3)
+    tokens = random_tokens(cfg["vocab"], n, 5)
+    want = plain.forward_logits(cfg, weights, tokens)
+    for cuts in ([n], [n - 40], [1100, 200, 33]):
+        logits_close(run(model, cache, tokens, cuts), want, dtype, f"cuts {cuts}")
     assert all(g.pages.n_free == g.pages.n_pages for g in cache.kv_groups)
 
 
