@@ -274,6 +274,19 @@ moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ dest, const 
     // an output that every token gets beside its chosen ones (`extra`), under a sigmoid gate of one logit per token: given,
     // or formed here as the token's row times the gate's weights (float32 sums in a fixed order)
     constexpr int V = 16 / (int)sizeof(T);
+    // the rows of the token's pairs and their weights are asked for first: two loads that hang on each other, on their way
+    // while the gate's logit is formed
+    const bool wide = width % V == 0 && top <= MOE_MAX_TOP && (((uintptr_t)y | (uintptr_t)out | (uintptr_t)extra) & 15) == 0;
+    int row[MOE_MAX_TOP];
+    float rw[MOE_MAX_TOP];
+    if (wide) {
+#pragma unroll
+        for (int k = 0; k < MOE_MAX_TOP; ++k)
+            if (k < top) {
+                row[k] = dest[t * top + k];
+                rw[k] = scale_output ? sorted_weight[row[k]] : 1.f;
+            }
+    }
     float share = extra ? 1.f : 0.f;
     if (extra && extra_gate) share = 1.f / (1.f + expf(-extra_gate[t]));
     if (extra && gate_weight) {
@@ -292,16 +305,8 @@ moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ dest, const 
         }
         share = 1.f / (1.f + expf(-block_sum(sum, scratch)));
     }
-    if (width % V == 0 && top <= MOE_MAX_TOP && (((uintptr_t)y | (uintptr_t)out | (uintptr_t)extra) & 15) == 0) {
-        // the same sums, 16 bytes of every row at a time; the rows and their weights are looked up once
-        int row[MOE_MAX_TOP];
-        float rw[MOE_MAX_TOP];
-#pragma unroll
-        for (int k = 0; k < MOE_MAX_TOP; ++k)
-            if (k < top) {
-                row[k] = dest[t * top + k];
-                rw[k] = scale_output ? sorted_weight[row[k]] : 1.f;
-            }
+    if (wide) {
+        // the same sums, 16 bytes of every row at a time
         for (int c = threadIdx.x * V; c < width; c += blockDim.x * V) {
             float sum[V];
 #pragma unroll
