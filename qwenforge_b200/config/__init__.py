@@ -6,10 +6,11 @@ from .qwen2 import Qwen2Config
 from .mefepel import MefepelConfig
 from .zebovik import ZebovikConfig
 from .rarevik import RarevikConfig
+from .gatosun import GatosunConfig
 from .presets import preset_config, preset_dict, preset_names
 
 __all__ = [
     "resolve_dtype", "ModelConfig", "config_class_for", "config_from_dict", "load_config", "register_architecture",
-    "registered_architectures", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "Qwen2Config", "MefepelConfig", "ZebovikConfig", "RarevikConfig",
+    "registered_architectures", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "Qwen2Config", "MefepelConfig", "ZebovikConfig", "RarevikConfig", "GatosunConfig",
     "preset_config", "preset_dict", "preset_names",
 ]

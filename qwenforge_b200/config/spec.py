@@ -36,6 +36,8 @@ class LayerSpec:
     """
     block: str
     parts: Mapping[str, PartSpec] = field(default_factory=dict)
+    # constants of the arrangement itself (say, a factor under which every sublayer's output enters the stream)
+    params: Mapping[str, Any] = field(default_factory=dict)
 
     def part(self, name: str) -> PartSpec:
         try:

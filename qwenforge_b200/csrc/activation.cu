@@ -133,7 +133,7 @@ QF_EXPORT int qf_scaled_swiglu(int is_bf16, const void* gu, const float* row_sca
 }
 
 // out = act(x + bias): the first half of a feed-forward without a gate. kind 0: the square of relu, 1: tanh-GELU,
-// 2: silu, 3: relu, 4: GELU in its exact form, z Phi(z) through erf. Float32 inside; bias may be null.
+// 2: silu, 3: relu, 4: GELU in its exact form, z Phi(z) through erf, 5: tanh. Float32 inside; bias may be null.
 __device__ __forceinline__ float activate(float z, int kind) {
     if (kind == 0) {
         const float r = fmaxf(z, 0.f);
@@ -142,6 +142,7 @@ __device__ __forceinline__ float activate(float z, int kind) {
     if (kind == 1) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
     if (kind == 2) return z / (1.f + expf(-z));
     if (kind == 4) return 0.5f * z * (1.f + erff(z * 0.7071067811865476f));
+    if (kind == 5) return tanhf(z);
     return fmaxf(z, 0.f);
 }
 
@@ -180,7 +181,7 @@ QF_EXPORT int qf_bias_act(int is_bf16, const void* x, const void* bias, void* ou
                           cudaStream_t stream) {
     const size_t total = (size_t)rows * width;
     if (total == 0) return 0;
-    if (kind < 0 || kind > 4) return (int)cudaErrorInvalidValue;
+    if (kind < 0 || kind > 5) return (int)cudaErrorInvalidValue;
     const size_t most = (size_t)(qf_sm_count() > 0 ? qf_sm_count() : 1) * 16;
     const int blocks = (int)((total + 255) / 256 < most ? (total + 255) / 256 : most);
     if (is_bf16 && width % 8 == 0 && ((uintptr_t)x | (uintptr_t)out | (uintptr_t)bias) % 16 == 0) {
@@ -262,4 +263,71 @@ QF_EXPORT int qf_head_gate(int is_bf16, void* x, const void* gate, int gate_stri
                                n_heads, head_dim, total);
     return (int)launch_pdl(head_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)x, (const float*)gate, gate_stride,
                            n_heads, head_dim, total);
+}
+
+// A gated feed-forward's middle with any of the activations above and optional biases: from the fused [gate | up] product,
+//   out[t][i] = act(gate[t][i] + bias[i]) * (up[t][i] + bias[inter + i]),  float32 inside.
+template <typename T>
+__global__ void __launch_bounds__(256)
+bias_glu_kernel(const T* __restrict__ gu, const T* __restrict__ bias, T* __restrict__ out, int inter, size_t total, int kind) {
+    grid_chain_entry();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / inter, c = i % inter;
+        float g = Num<T>::to_f(gu[t * 2 * inter + c]), u = Num<T>::to_f(gu[t * 2 * inter + inter + c]);
+        if (bias) {
+            g += Num<T>::to_f(bias[c]);
+            u += Num<T>::to_f(bias[inter + c]);
+        }
+        out[i] = Num<T>::from_f(activate(g, kind) * u);
+    }
+}
+
+// Eight bf16 elements per thread; needs inter % 8 == 0 and 16-byte aligned pointers.
+__global__ void __launch_bounds__(256)
+bias_glu_bf16x8_kernel(const bf16* __restrict__ gu, const bf16* __restrict__ bias, bf16* __restrict__ out, int inter, size_t total8,
+                       int kind) {
+    grid_chain_entry();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i * 8 / inter, c = i * 8 % inter;
+        const uint4 g4 = *reinterpret_cast<const uint4*>(gu + t * 2 * inter + c);
+        const uint4 u4 = *reinterpret_cast<const uint4*>(gu + t * 2 * inter + inter + c);
+        uint4 bg4 = make_uint4(0u, 0u, 0u, 0u), bu4 = bg4;
+        if (bias) {
+            bg4 = *reinterpret_cast<const uint4*>(bias + c);
+            bu4 = *reinterpret_cast<const uint4*>(bias + inter + c);
+        }
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
+        const __nv_bfloat162* bg2 = reinterpret_cast<const __nv_bfloat162*>(&bg4);
+        const __nv_bfloat162* bu2 = reinterpret_cast<const __nv_bfloat162*>(&bu4);
+        uint4 o4;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
+            const float2 bg = __bfloat1622float2(bg2[j]), bu = __bfloat1622float2(bu2[j]);
+            o2[j] = __floats2bfloat162_rn(activate(g.x + bg.x, kind) * (u.x + bu.x), activate(g.y + bg.y, kind) * (u.y + bu.y));
+        }
+        *reinterpret_cast<uint4*>(out + i * 8) = o4;
+    }
+}
+
+QF_EXPORT int qf_bias_glu(int is_bf16, const void* gu, const void* bias, void* out, int rows, int inter, int kind,
+                          cudaStream_t stream) {
+    const size_t total = (size_t)rows * inter;
+    if (total == 0) return 0;
+    if (kind < 0 || kind > 5) return (int)cudaErrorInvalidValue;
+    const size_t most = (size_t)(qf_sm_count() > 0 ? qf_sm_count() : 1) * 16;
+    if (is_bf16 && inter % 8 == 0 && ((uintptr_t)gu | (uintptr_t)out | (uintptr_t)bias) % 16 == 0) {
+        const size_t total8 = total / 8;
+        const int b8 = (int)((total8 + 255) / 256 < most ? (total8 + 255) / 256 : most);
+        return (int)launch_pdl(bias_glu_bf16x8_kernel, dim3(b8), dim3(256), 0, stream, (const bf16*)gu, (const bf16*)bias, (bf16*)out,
+                               inter, total8, kind);
+    }
+    const int blocks = (int)((total + 255) / 256 < most ? (total + 255) / 256 : most);
+    if (is_bf16)
+        return (int)launch_pdl(bias_glu_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)gu, (const bf16*)bias, (bf16*)out,
+                               inter, total, kind);
+    return (int)launch_pdl(bias_glu_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, (const float*)bias, (float*)out,
+                           inter, total, kind);
 }

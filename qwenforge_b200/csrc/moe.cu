@@ -53,6 +53,69 @@ __device__ __forceinline__ void moe_choose(const float* z_raw, const float* bias
         for (int k = 0; k < top; ++k) weight[k] /= total;
 }
 
+// The choice among groups of neighbouring experts, with a correction that steers the choice and not the weights:
+//   s_e = sigmoid(z_e);  c_e = s_e + correction_e (the choice score);  the experts form `group_count` equal groups of
+//   neighbours, a group's score is the sum of its two largest c (of its one, in groups of one);  only experts of the
+//   `group_keep` groups with the largest scores can be chosen;  among them the `top` largest c;  weights s_e, divided by
+//   their sum with `renormalize`.  Ties go to the lower index.  (group_count 1: no groups.)
+struct MoeGroups {
+    const float* correction;   // float32 [experts] or null
+    int count, keep;
+};
+#define MOE_MAX_GROUPS 64
+
+__device__ __forceinline__ void moe_choose_grouped(const float* z_raw, const float* bias, int n_experts, int top, int renormalize,
+                                                   MoeGroups groups, int* chosen, float* weight) {
+    auto score = [&](int e) { return 1.0f / (1.0f + expf(-(bias ? z_raw[e] + bias[e] : z_raw[e]))); };
+    auto choice = [&](int e) { return groups.correction ? score(e) + groups.correction[e] : score(e); };
+    unsigned long long kept = ~0ull;
+    const int size = n_experts / groups.count;
+    if (groups.count > 1 && groups.keep < groups.count) {
+        float group_score[MOE_MAX_GROUPS];
+        for (int g = 0; g < groups.count; ++g) {
+            float first = -FLT_MAX, second = -FLT_MAX;
+            for (int e = g * size; e < (g + 1) * size; ++e) {
+                const float c = choice(e);
+                if (c > first) {
+                    second = first;
+                    first = c;
+                } else if (c > second) {
+                    second = c;
+                }
+            }
+            group_score[g] = size > 1 ? first + second : first;
+        }
+        kept = 0ull;
+        for (int k = 0; k < groups.keep; ++k) {
+            int best = -1;
+            for (int g = 0; g < groups.count; ++g)
+                if (!((kept >> g) & 1ull) && (best < 0 || group_score[g] > group_score[best])) best = g;
+            kept |= 1ull << best;
+        }
+    }
+    float total = 0.f;
+    for (int k = 0; k < top; ++k) {
+        int best = -1;
+        float best_c = -FLT_MAX;
+        for (int e = 0; e < n_experts; ++e) {
+            if (groups.count > 1 && !((kept >> (e / size)) & 1ull)) continue;
+            bool taken = false;
+            for (int j = 0; j < k; ++j) taken |= chosen[j] == e;
+            if (taken) continue;
+            const float c = choice(e);
+            if (best < 0 || c > best_c) {
+                best = e;
+                best_c = c;
+            }
+        }
+        chosen[k] = best;
+        weight[k] = score(best);
+        total += weight[k];
+    }
+    if (renormalize)
+        for (int k = 0; k < top; ++k) weight[k] /= total;
+}
+
 // Scratch in pair order (pair = token * top + k): pair_expert, pair_weight. Results: dest [pairs] (the row of every pair),
 // and in row order sorted_token [pairs], sorted_weight float32 [pairs]; offsets [experts + 1]; tile_group, tile_row0
 // [max_tiles]; n_tiles [1].
@@ -62,7 +125,7 @@ moe_plan_kernel(const float* logits, int n_tokens, int n_experts, int top, int s
                 float* __restrict__ sorted_weight, int* __restrict__ dest, int* __restrict__ offsets,
                 int* __restrict__ tile_group, int* __restrict__ tile_row0, int* __restrict__ n_tiles, int max_tiles,
                 int tile_rows, const void* __restrict__ x, const void* __restrict__ router, int width, int x_is_bf16,
-                const float* __restrict__ bias) {
+                const float* __restrict__ bias, MoeGroups groups) {
     grid_chain_entry();
     extern __shared__ int shared[];
     int* counts = shared;                   // [experts]: rows per expert, then every expert's first row
@@ -126,7 +189,8 @@ moe_plan_kernel(const float* logits, int n_tokens, int n_experts, int top, int s
     for (int t = threadIdx.x; t < n_tokens; t += blockDim.x) {
         int chosen[MOE_MAX_TOP];
         float weight[MOE_MAX_TOP];
-        moe_choose(logits + (size_t)t * n_experts, bias, n_experts, top, softmax_scores, renormalize, chosen, weight);
+        if (groups.count > 0) moe_choose_grouped(logits + (size_t)t * n_experts, bias, n_experts, top, renormalize, groups, chosen, weight);
+        else moe_choose(logits + (size_t)t * n_experts, bias, n_experts, top, softmax_scores, renormalize, chosen, weight);
         for (int k = 0; k < top; ++k) {
             const int pair = t * top + k;
             pair_expert[pair] = chosen[k];
@@ -175,7 +239,7 @@ moe_plan_kernel(const float* logits, int n_tokens, int n_experts, int top, int s
 __global__ void __launch_bounds__(256)
 moe_route_kernel(const float* __restrict__ logits, int n_tokens, int n_experts, int top, int softmax_scores, int renormalize,
                  int* __restrict__ pair_expert, float* __restrict__ pair_weight, int* __restrict__ dest,
-                 int* __restrict__ expert_rows, const float* __restrict__ bias) {
+                 int* __restrict__ expert_rows, const float* __restrict__ bias, MoeGroups groups) {
     grid_chain_entry();
     extern __shared__ int shared[];
     int* counts = shared;               // [experts] pairs of this block
@@ -186,7 +250,8 @@ moe_route_kernel(const float* __restrict__ logits, int n_tokens, int n_experts, 
     int chosen[MOE_MAX_TOP], rank[MOE_MAX_TOP];
     float weight[MOE_MAX_TOP];
     if (t < n_tokens) {
-        moe_choose(logits + (size_t)t * n_experts, bias, n_experts, top, softmax_scores, renormalize, chosen, weight);
+        if (groups.count > 0) moe_choose_grouped(logits + (size_t)t * n_experts, bias, n_experts, top, renormalize, groups, chosen, weight);
+        else moe_choose(logits + (size_t)t * n_experts, bias, n_experts, top, softmax_scores, renormalize, chosen, weight);
         for (int k = 0; k < top; ++k) rank[k] = atomicAdd(&counts[chosen[k]], 1);
     }
     __syncthreads();
@@ -349,18 +414,35 @@ moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ dest, const 
 // is given, or x [n_tokens][width] and router [n_experts][width] (both bfloat16 or both float32), from which the kernel makes
 // the logits itself in shared memory (n_tokens * n_experts <= 8192).
 // bias: float32 [n_experts] added to the logits, or null.
-QF_EXPORT int qf_moe_plan_biased(const float* logits, int n_tokens, int n_experts, int top, int softmax_scores, int renormalize,
-                                 int* pair_expert, float* pair_weight, int* sorted_token, float* sorted_weight, int* dest,
-                                 int* offsets, int* tile_group, int* tile_row0, int* n_tiles, int max_tiles, int tile_rows,
-                                 const void* x, const void* router, int width, int x_is_bf16, const float* bias,
-                                 cudaStream_t stream) {
+// correction (float32 [n_experts] or null), group_count, group_keep: the choice among groups of neighbouring experts
+// (`moe_choose_grouped`; sigmoid scores); group_count 0: the plain choice.
+QF_EXPORT int qf_moe_plan_grouped(const float* logits, int n_tokens, int n_experts, int top, int softmax_scores, int renormalize,
+                                  int* pair_expert, float* pair_weight, int* sorted_token, float* sorted_weight, int* dest,
+                                  int* offsets, int* tile_group, int* tile_row0, int* n_tiles, int max_tiles, int tile_rows,
+                                  const void* x, const void* router, int width, int x_is_bf16, const float* bias,
+                                  const float* correction, int group_count, int group_keep, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
+    if (group_count < 0 || group_count > MOE_MAX_GROUPS || (group_count > 0 && (n_experts % group_count || group_keep < 1 ||
+        group_keep > group_count || (long long)group_keep * (n_experts / group_count) < top || softmax_scores)))
+        return (int)cudaErrorInvalidValue;
+    const MoeGroups groups = {correction, group_count, group_keep};
     if (top < 1 || top > MOE_MAX_TOP || top > n_experts || n_experts > 8192 || tile_rows <= 0) return (int)cudaErrorInvalidValue;
     if (!logits && !(x && router && (long long)n_tokens * n_experts <= 8192)) return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)(2 * n_experts + 1) * sizeof(int) + (logits ? 0 : (size_t)n_tokens * n_experts * sizeof(float));
     return (int)launch_pdl(moe_plan_kernel, dim3(1), dim3(MOE_PLAN_THREADS), smem, stream, logits, n_tokens, n_experts, top,
                            softmax_scores, renormalize, pair_expert, pair_weight, sorted_token, sorted_weight, dest, offsets,
-                           tile_group, tile_row0, n_tiles, max_tiles, tile_rows, logits ? nullptr : x, router, width, x_is_bf16, bias);
+                           tile_group, tile_row0, n_tiles, max_tiles, tile_rows, logits ? nullptr : x, router, width, x_is_bf16, bias,
+                           groups);
+}
+
+QF_EXPORT int qf_moe_plan_biased(const float* logits, int n_tokens, int n_experts, int top, int softmax_scores, int renormalize,
+                                 int* pair_expert, float* pair_weight, int* sorted_token, float* sorted_weight, int* dest,
+                                 int* offsets, int* tile_group, int* tile_row0, int* n_tiles, int max_tiles, int tile_rows,
+                                 const void* x, const void* router, int width, int x_is_bf16, const float* bias,
+                                 cudaStream_t stream) {
+    return qf_moe_plan_grouped(logits, n_tokens, n_experts, top, softmax_scores, renormalize, pair_expert, pair_weight, sorted_token,
+                               sorted_weight, dest, offsets, tile_group, tile_row0, n_tiles, max_tiles, tile_rows, x, router, width,
+                               x_is_bf16, bias, nullptr, 0, 0, stream);
 }
 
 QF_EXPORT int qf_moe_plan(const float* logits, int n_tokens, int n_experts, int top, int softmax_scores, int renormalize,
@@ -405,16 +487,21 @@ QF_EXPORT int qf_moe_combine(int is_bf16, const void* y, const int* dest, const 
 }
 
 // The plan of a long step by three launches (see moe_route_kernel). expert_rows: int32 [n_experts], zero before the call.
-QF_EXPORT int qf_moe_plan_long_biased(const float* logits, int n_tokens, int n_experts, int top, int softmax_scores,
-                                      int renormalize, int* pair_expert, float* pair_weight, int* sorted_token,
-                                      float* sorted_weight, int* dest, int* offsets, int* tile_group, int* tile_row0, int* n_tiles,
-                                      int max_tiles, int tile_rows, int* expert_rows, const float* bias, cudaStream_t stream) {
+QF_EXPORT int qf_moe_plan_long_grouped(const float* logits, int n_tokens, int n_experts, int top, int softmax_scores,
+                                       int renormalize, int* pair_expert, float* pair_weight, int* sorted_token,
+                                       float* sorted_weight, int* dest, int* offsets, int* tile_group, int* tile_row0, int* n_tiles,
+                                       int max_tiles, int tile_rows, int* expert_rows, const float* bias, const float* correction,
+                                       int group_count, int group_keep, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
+    if (group_count < 0 || group_count > MOE_MAX_GROUPS || (group_count > 0 && (n_experts % group_count || group_keep < 1 ||
+        group_keep > group_count || (long long)group_keep * (n_experts / group_count) < top || softmax_scores)))
+        return (int)cudaErrorInvalidValue;
+    const MoeGroups groups = {correction, group_count, group_keep};
     if (top < 1 || top > MOE_MAX_TOP || top > n_experts || n_experts > 4096 || tile_rows <= 0 || !logits || !expert_rows)
         return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)(2 * n_experts + 1) * sizeof(int);
     int code = (int)launch_pdl(moe_route_kernel, dim3((n_tokens + 255) / 256), dim3(256), smem, stream, logits, n_tokens, n_experts,
-                               top, softmax_scores, renormalize, pair_expert, pair_weight, dest, expert_rows, bias);
+                               top, softmax_scores, renormalize, pair_expert, pair_weight, dest, expert_rows, bias, groups);
     if (code) return code;
     code = (int)launch_pdl(moe_offsets_kernel, dim3(1), dim3(256), smem, stream, (const int*)expert_rows, n_experts, offsets,
                            tile_group, tile_row0, n_tiles, max_tiles, tile_rows);
@@ -422,6 +509,15 @@ QF_EXPORT int qf_moe_plan_long_biased(const float* logits, int n_tokens, int n_e
     const int pairs = n_tokens * top;
     return (int)launch_pdl(moe_place_kernel, dim3((pairs + 255) / 256), dim3(256), 0, stream, (const int*)pair_expert,
                            (const float*)pair_weight, (const int*)offsets, dest, sorted_token, sorted_weight, pairs, top);
+}
+
+QF_EXPORT int qf_moe_plan_long_biased(const float* logits, int n_tokens, int n_experts, int top, int softmax_scores,
+                                      int renormalize, int* pair_expert, float* pair_weight, int* sorted_token,
+                                      float* sorted_weight, int* dest, int* offsets, int* tile_group, int* tile_row0, int* n_tiles,
+                                      int max_tiles, int tile_rows, int* expert_rows, const float* bias, cudaStream_t stream) {
+    return qf_moe_plan_long_grouped(logits, n_tokens, n_experts, top, softmax_scores, renormalize, pair_expert, pair_weight,
+                                    sorted_token, sorted_weight, dest, offsets, tile_group, tile_row0, n_tiles, max_tiles, tile_rows,
+                                    expert_rows, bias, nullptr, 0, 0, stream);
 }
 
 QF_EXPORT int qf_moe_plan_long(const float* logits, int n_tokens, int n_experts, int top, int softmax_scores, int renormalize,

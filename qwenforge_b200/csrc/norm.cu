@@ -458,3 +458,183 @@ QF_EXPORT int qf_stream_pair(int is_bf16, const float* hidden, const void* a, co
     return (int)launch_pdl(stream_pair_kernel<float>, dim3(elementwise_blocks(total)), dim3(256), 0, stream, hidden, (const float*)a,
                            (const float*)b, other, (float*)out, total, width);
 }
+
+// ------------------------------------------------------------------------------------------------------------------
+// Sublayer outputs that enter the stream under a factor each (a residual multiplier, the weights of two mixers that run
+// side by side):   hidden += sa * a + sb * b   (b may be absent), then the RMS norm of the stream as above. The products,
+// their sum, the addition and the statistics are float32; one order of operations in every kernel below:
+//   t = sa * a;  t = fma(sb, b, t);  hidden = hidden + t.
+template <typename T>
+__device__ __forceinline__ float scaled_terms(const T* a, float sa, const T* b, float sb, size_t i) {
+    float t = sa * Num<T>::to_f(a[i]);
+    if (b) t = fmaf(sb, Num<T>::to_f(b[i]), t);
+    return t;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+add_scaled_rms_norm_kernel(float* __restrict__ hidden, const T* __restrict__ a, float sa, const T* __restrict__ b, float sb,
+                           const T* __restrict__ weight, T* __restrict__ out, int width, float eps) {
+    grid_chain_entry();
+    __shared__ float scratch[33];
+    const size_t row0 = (size_t)blockIdx.x * width;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float v = hidden[row0 + c] + scaled_terms(a, sa, b, sb, row0 + c);
+        hidden[row0 + c] = v;
+        ss += v * v;
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)width + eps);
+    for (int c = threadIdx.x; c < width; c += blockDim.x)
+        out[row0 + c] = Num<T>::from_f(hidden[row0 + c] * inv * Num<T>::to_f(weight[c]));
+}
+
+// Narrow rows (width <= 1024, a multiple of 4, 16-byte aligned): a warp per row, the row in the lanes' registers.
+template <typename T>
+__global__ void __launch_bounds__(NW_ROWS * 32)
+add_scaled_rms_norm_warp_kernel(float* __restrict__ hidden, const T* __restrict__ a, float sa, const T* __restrict__ b, float sb,
+                                const T* __restrict__ weight, T* __restrict__ out, int rows, int width, float eps) {
+    grid_chain_entry();
+    const int row = blockIdx.x * NW_ROWS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const size_t row0 = (size_t)row * width;
+    const int n4 = width / 4;
+    float4 v[NW_MAX], av[NW_MAX], bv[NW_MAX];
+#pragma unroll
+    for (int u = 0; u < NW_MAX; ++u) {
+        const int c = lane + 32 * u;
+        const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+        v[u] = c < n4 ? Vec4<float>::load(hidden + row0 + 4 * c) : zero;
+        av[u] = c < n4 ? Vec4<T>::load(a + row0 + 4 * c) : zero;
+        bv[u] = (b && c < n4) ? Vec4<T>::load(b + row0 + 4 * c) : zero;
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int u = 0; u < NW_MAX; ++u) {
+        const int c = lane + 32 * u;
+        if (c < n4) {
+            float4 t = make_float4(sa * av[u].x, sa * av[u].y, sa * av[u].z, sa * av[u].w);
+            if (b) t = make_float4(fmaf(sb, bv[u].x, t.x), fmaf(sb, bv[u].y, t.y), fmaf(sb, bv[u].z, t.z), fmaf(sb, bv[u].w, t.w));
+            v[u].x += t.x;
+            v[u].y += t.y;
+            v[u].z += t.z;
+            v[u].w += t.w;
+            Vec4<float>::store(hidden + row0 + 4 * c, v[u]);
+        }
+        ss += v[u].x * v[u].x + v[u].y * v[u].y + v[u].z * v[u].z + v[u].w * v[u].w;
+    }
+    const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)width + eps);
+#pragma unroll
+    for (int u = 0; u < NW_MAX; ++u) {
+        const int c = lane + 32 * u;
+        if (c < n4) {
+            const float4 w = Vec4<T>::load(weight + 4 * c);
+            Vec4<T>::store(out + row0 + 4 * c, make_float4(v[u].x * inv * w.x, v[u].y * inv * w.y, v[u].z * inv * w.z, v[u].w * inv * w.w));
+        }
+    }
+}
+
+template <typename T>
+static int launch_scaled_norm(float* hidden, const void* a, float sa, const void* b, float sb, const void* weight, void* out,
+                              int rows, int width, float eps, cudaStream_t stream) {
+    const uintptr_t align = (uintptr_t)hidden | (uintptr_t)a | (uintptr_t)b | (uintptr_t)weight | (uintptr_t)out;
+    if (width % 4 == 0 && width <= 4 * 32 * NW_MAX && align % 16 == 0)
+        return (int)launch_pdl(add_scaled_rms_norm_warp_kernel<T>, dim3((rows + NW_ROWS - 1) / NW_ROWS), dim3(NW_ROWS * 32), 0, stream,
+                               hidden, (const T*)a, sa, (const T*)b, sb, (const T*)weight, (T*)out, rows, width, eps);
+    return (int)launch_pdl(add_scaled_rms_norm_kernel<T>, dim3(rows), dim3(256), 0, stream, hidden, (const T*)a, sa, (const T*)b, sb,
+                           (const T*)weight, (T*)out, width, eps);
+}
+
+// hidden float32 [rows][width]; a (required), b (or null), weight, out in the activation type.
+QF_EXPORT int qf_add_scaled_rms_norm(int is_bf16, float* hidden, const void* a, float sa, const void* b, float sb,
+                                     const void* weight, void* out, int rows, int width, float eps, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (!a) return (int)cudaErrorInvalidValue;
+    return is_bf16 ? launch_scaled_norm<bf16>(hidden, a, sa, b, sb, weight, out, rows, width, eps, stream)
+                   : launch_scaled_norm<float>(hidden, a, sa, b, sb, weight, out, rows, width, eps, stream);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+residual_add_scaled_kernel(float* __restrict__ hidden, const T* __restrict__ a, float sa, const T* __restrict__ b, float sb,
+                           size_t total) {
+    grid_chain_entry();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+        hidden[i] += scaled_terms(a, sa, b, sb, i);
+}
+
+QF_EXPORT int qf_residual_add_scaled(int is_bf16, float* hidden, const void* a, float sa, const void* b, float sb, long long n,
+                                     cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (!a) return (int)cudaErrorInvalidValue;
+    if (is_bf16)
+        return (int)launch_pdl(residual_add_scaled_kernel<bf16>, dim3(elementwise_blocks((size_t)n)), dim3(256), 0, stream, hidden,
+                               (const bf16*)a, sa, (const bf16*)b, sb, (size_t)n);
+    return (int)launch_pdl(residual_add_scaled_kernel<float>, dim3(elementwise_blocks((size_t)n)), dim3(256), 0, stream, hidden,
+                           (const float*)a, sa, (const float*)b, sb, (size_t)n);
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// RMS norms over runs of columns of wider rows, in place: for each of up to two runs (say the query columns and the key
+// columns of one projection's output), x[t][col0 .. col0 + width) <- x / sqrt(sum(x^2) / count + eps) * weight. `count` is
+// how many of the run's columns carry numbers (columns of padding hold zeros and add nothing to the sum). Statistics and
+// scaling are float32. A block per (row, run).
+struct ColsRun {
+    int col0, width, count;
+    const void* weight;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+rms_norm_cols_kernel(T* __restrict__ x, int ld, ColsRun r0, ColsRun r1, float eps) {
+    grid_chain_entry();
+    __shared__ float scratch[33];
+    const ColsRun r = blockIdx.y == 0 ? r0 : r1;
+    T* row = x + (size_t)blockIdx.x * ld + r.col0;
+    const T* w = (const T*)r.weight;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < r.width; c += blockDim.x) {
+        const float v = Num<T>::to_f(row[c]);
+        ss += v * v;
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)r.count + eps);
+    for (int c = threadIdx.x; c < r.width; c += blockDim.x) row[c] = Num<T>::from_f(Num<T>::to_f(row[c]) * inv * Num<T>::to_f(w[c]));
+}
+
+QF_EXPORT int qf_rms_norm_cols(int is_bf16, void* x, int ld, int rows, int n_runs, int col0_a, int width_a, int count_a,
+                               const void* weight_a, int col0_b, int width_b, int count_b, const void* weight_b, float eps,
+                               cudaStream_t stream) {
+    if (rows <= 0 || n_runs <= 0) return 0;
+    if (n_runs > 2 || count_a <= 0 || (n_runs == 2 && count_b <= 0)) return (int)cudaErrorInvalidValue;
+    const ColsRun a = {col0_a, width_a, count_a, weight_a}, b = {col0_b, width_b, count_b, weight_b};
+    if (is_bf16) return (int)launch_pdl(rms_norm_cols_kernel<bf16>, dim3(rows, n_runs), dim3(128), 0, stream, (bf16*)x, ld, a, b, eps);
+    return (int)launch_pdl(rms_norm_cols_kernel<float>, dim3(rows, n_runs), dim3(128), 0, stream, (float*)x, ld, a, b, eps);
+}
+
+// Rows drawn towards another layer's rows of the same tokens, head by head, in place:
+//   x[t][h * x_head + c] <- (1 - lambda) * x[..] + lambda * other[t][h * other_head + c],   c < size   (float32 inside)
+template <typename T>
+__global__ void __launch_bounds__(256)
+mix_rows_kernel(T* __restrict__ x, int ldx, const T* __restrict__ other, int ldo, int heads, int size, int x_head, int other_head,
+                float lambda, size_t total) {
+    grid_chain_entry();
+    const float keep = 1.0f - lambda;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / ((size_t)heads * size);
+        const int rest = (int)(i % ((size_t)heads * size)), h = rest / size, c = rest % size;
+        T* p = x + t * ldx + (size_t)h * x_head + c;
+        const float mine = Num<T>::to_f(*p), theirs = Num<T>::to_f(other[t * ldo + (size_t)h * other_head + c]);
+        *p = Num<T>::from_f(fmaf(lambda, theirs, keep * mine));
+    }
+}
+
+QF_EXPORT int qf_mix_rows(int is_bf16, void* x, int ldx, const void* other, int ldo, int rows, int heads, int size, int x_head,
+                          int other_head, float lambda, cudaStream_t stream) {
+    const size_t total = (size_t)rows * heads * size;
+    if (total == 0) return 0;
+    if (is_bf16)
+        return (int)launch_pdl(mix_rows_kernel<bf16>, dim3(elementwise_blocks(total)), dim3(256), 0, stream, (bf16*)x, ldx,
+                               (const bf16*)other, ldo, heads, size, x_head, other_head, lambda, total);
+    return (int)launch_pdl(mix_rows_kernel<float>, dim3(elementwise_blocks(total)), dim3(256), 0, stream, (float*)x, ldx,
+                           (const float*)other, ldo, heads, size, x_head, other_head, lambda, total);
+}

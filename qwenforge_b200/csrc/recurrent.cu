@@ -135,13 +135,18 @@ __device__ __forceinline__ float load_early(const bf16* p) {
 #define SCAN_TOKENS 32
 #define SCAN_COLS 16
 
-template <typename T, int WARPS, int ROWS>
+// MODE 0: one decay and one take per (token, head), the output read from the state AFTER the token (the form above).
+// MODE 1: a decay per (token, head, row of S) (`decay` is [T][heads * dim]), take 1, the output read after the token:
+//         S <- diag(w_t) S + k_t v_t^T,  y_t = S^T q_t.
+// MODE 2: the same update, but the output is read BEFORE it and the token's own outer product enters under a learned
+//         factor per row (`bonus`, float32 [heads][dim]):  y_t = (S + diag(u) k_t v_t^T)^T q_t,  then the update.
+template <typename T, int WARPS, int ROWS, int MODE>
 __global__ void __launch_bounds__(32 * WARPS)
 outer_state_scan_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_stride, const T* __restrict__ v,
                         int v_stride, const float* __restrict__ decay, const float* __restrict__ take,
                         const int* __restrict__ cu_q, const int* __restrict__ slots, float* __restrict__ state,
                         long long slot_stride, long long s_offset, long long n_offset, int n_heads, int n_groups, int dim,
-                        int vdim, float q_scale, float* __restrict__ y, float* __restrict__ nq) {
+                        int vdim, float q_scale, float* __restrict__ y, float* __restrict__ nq, const float* __restrict__ bonus) {
     grid_chain_entry();
     extern __shared__ __align__(16) float scan_smem[];
     constexpr int THREADS = 32 * WARPS, PARTS = 2 * WARPS, padded = PARTS * ROWS;   // padded >= dim
@@ -151,6 +156,7 @@ outer_state_scan_kernel(const T* __restrict__ q, int q_stride, const T* __restri
     float* part_s = v_s + SCAN_TOKENS * SCAN_COLS;                   // [PARTS][SCAN_TOKENS][SCAN_COLS]
     float* decay_s = part_s + PARTS * SCAN_TOKENS * SCAN_COLS;       // [SCAN_TOKENS]
     float* take_s = decay_s + SCAN_TOKENS;                           // [SCAN_TOKENS]
+    float* w_s = take_s + SCAN_TOKENS;                               // [SCAN_TOKENS][padded], MODE 1 and 2: a decay per row
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, head = blockIdx.y, seq = blockIdx.z;
     const int c16 = lane & 15, part = warp * 2 + (lane >> 4);
     const int col = blockIdx.x * SCAN_COLS + c16;           // column of S; vdim is the column of n
@@ -176,6 +182,11 @@ outer_state_scan_kernel(const T* __restrict__ q, int q_stride, const T* __restri
     constexpr int QK_EACH = SCAN_TOKENS * padded / THREADS;
     constexpr int V_EACH = (SCAN_TOKENS * SCAN_COLS + THREADS - 1) / THREADS;
     float q_next[QK_EACH], k_next[QK_EACH], v_next[V_EACH], gate_next[2] = {0.f, 0.f};
+    float w_next[MODE != 0 ? QK_EACH : 1], u_row[MODE == 2 ? ROWS : 1];
+    if constexpr (MODE == 2) {
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) u_row[r] = d0 + r < dim ? bonus[(size_t)head * dim + d0 + r] : 0.f;
+    }
     auto fetch = [&](int t0) {
         const int n_here = min(SCAN_TOKENS, end - t0);
 #pragma unroll
@@ -185,6 +196,7 @@ outer_state_scan_kernel(const T* __restrict__ q, int q_stride, const T* __restri
             const size_t t = t0 + j;
             q_next[u] = there ? load_early(q + t * q_stride + group * dim + d) * q_scale : 0.f;
             k_next[u] = there ? load_early(k + t * k_stride + group * dim + d) : 0.f;
+            if constexpr (MODE != 0) w_next[u] = there ? load_early(decay + t * ((size_t)n_heads * dim) + (size_t)head * dim + d) : 0.f;
         }
 #pragma unroll
         for (int u = 0; u < V_EACH; ++u) {
@@ -193,7 +205,7 @@ outer_state_scan_kernel(const T* __restrict__ q, int q_stride, const T* __restri
             if (i < SCAN_TOKENS * SCAN_COLS && j < n_here)
                 v_next[u] = c < vdim ? load_early(v + (size_t)(t0 + j) * v_stride + head * vdim + c) : 1.f;
         }
-        if (threadIdx.x < n_here) {
+        if (MODE == 0 && threadIdx.x < n_here) {
             gate_next[0] = load_early(decay + (size_t)(t0 + threadIdx.x) * n_heads + head);
             gate_next[1] = load_early(take + (size_t)(t0 + threadIdx.x) * n_heads + head);
         }
@@ -203,6 +215,7 @@ outer_state_scan_kernel(const T* __restrict__ q, int q_stride, const T* __restri
         for (int u = 0; u < QK_EACH; ++u) {
             q_s[threadIdx.x + u * THREADS] = q_next[u];
             k_s[threadIdx.x + u * THREADS] = k_next[u];
+            if constexpr (MODE != 0) w_s[threadIdx.x + u * THREADS] = w_next[u];
         }
 #pragma unroll
         for (int u = 0; u < V_EACH; ++u) {
@@ -223,6 +236,38 @@ outer_state_scan_kernel(const T* __restrict__ q, int q_stride, const T* __restri
         __syncthreads();
         if (t0 + SCAN_TOKENS < end) fetch(t0 + SCAN_TOKENS);   // on its way while this tile is worked on
         auto token = [&](int j) {
+            if constexpr (MODE != 0) {
+                const float add = v_s[j * SCAN_COLS + c16];
+                const float* kj = k_s + j * padded + d0;
+                const float* qj = q_s + j * padded + d0;
+                const float* wj = w_s + j * padded + d0;
+                float4 kk[ROWS / 4], qq[ROWS / 4], ww[ROWS / 4];
+#pragma unroll
+                for (int r = 0; r < ROWS / 4; ++r) {
+                    kk[r] = *reinterpret_cast<const float4*>(kj + 4 * r);
+                    qq[r] = *reinterpret_cast<const float4*>(qj + 4 * r);
+                    ww[r] = *reinterpret_cast<const float4*>(wj + 4 * r);
+                }
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int r = 0; r < ROWS / 4; ++r) {
+                    const float kr[4] = {kk[r].x, kk[r].y, kk[r].z, kk[r].w}, qr[4] = {qq[r].x, qq[r].y, qq[r].z, qq[r].w};
+                    const float wr[4] = {ww[r].x, ww[r].y, ww[r].z, ww[r].w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float kv = add * kr[e];
+                        if constexpr (MODE == 2) {
+                            acc[e] = fmaf(fmaf(u_row[4 * r + e], kv, s[4 * r + e]), qr[e], acc[e]);
+                            s[4 * r + e] = fmaf(s[4 * r + e], wr[e], kv);
+                        } else {
+                            s[4 * r + e] = fmaf(s[4 * r + e], wr[e], kv);
+                            acc[e] = fmaf(s[4 * r + e], qr[e], acc[e]);
+                        }
+                    }
+                }
+                part_s[(part * SCAN_TOKENS + j) * SCAN_COLS + c16] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+                return;
+            }
             const float keep = decay_s[j], add = take_s[j] * v_s[j * SCAN_COLS + c16];
             const float* kj = k_s + j * padded + d0;
             const float* qj = q_s + j * padded + d0;
@@ -270,27 +315,27 @@ outer_state_scan_kernel(const T* __restrict__ q, int q_stride, const T* __restri
     }
 }
 
-template <typename T, int WARPS, int ROWS>
+template <typename T, int WARPS, int ROWS, int MODE>
 static int launch_scan(const void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride, const float* decay,
                        const float* take, const int* cu_q, const int* slots, int n_seqs, float* state, long long slot_stride,
                        long long s_offset, long long n_offset, int n_heads, int n_groups, int dim, int vdim, float q_scale,
-                       float* y, float* nq, cudaStream_t stream) {
+                       float* y, float* nq, const float* bonus, cudaStream_t stream) {
     const int columns = vdim + (n_offset >= 0 ? 1 : 0);
     constexpr int PARTS = 2 * WARPS, padded = PARTS * ROWS;
-    const size_t smem = (size_t)(2 * SCAN_TOKENS * padded + SCAN_TOKENS * SCAN_COLS + PARTS * SCAN_TOKENS * SCAN_COLS + 2 * SCAN_TOKENS) * sizeof(float);
-    cudaError_t e = cudaFuncSetAttribute(outer_state_scan_kernel<T, WARPS, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const size_t smem = (size_t)((MODE != 0 ? 3 : 2) * SCAN_TOKENS * padded + SCAN_TOKENS * SCAN_COLS + PARTS * SCAN_TOKENS * SCAN_COLS + 2 * SCAN_TOKENS) * sizeof(float);
+    cudaError_t e = cudaFuncSetAttribute(outer_state_scan_kernel<T, WARPS, ROWS, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    return (int)launch_pdl(outer_state_scan_kernel<T, WARPS, ROWS>, dim3((columns + SCAN_COLS - 1) / SCAN_COLS, n_heads, n_seqs),
+    return (int)launch_pdl(outer_state_scan_kernel<T, WARPS, ROWS, MODE>, dim3((columns + SCAN_COLS - 1) / SCAN_COLS, n_heads, n_seqs),
                            dim3(32 * WARPS), smem, stream, (const T*)q, q_stride, (const T*)k, k_stride, (const T*)v, v_stride, decay,
-                           take, cu_q, slots, state, slot_stride, s_offset, n_offset, n_heads, n_groups, dim, vdim, q_scale, y, nq);
+                           take, cu_q, slots, state, slot_stride, s_offset, n_offset, n_heads, n_groups, dim, vdim, q_scale, y, nq, bonus);
 }
 
 #define QF_SCAN_ARGS q, q_stride, k, k_stride, v, v_stride, decay, take, cu_q, slots, n_seqs, state, slot_stride, s_offset, \
-                     n_offset, n_heads, n_groups, dim, vdim, q_scale, y, nq, stream
+                     n_offset, n_heads, n_groups, dim, vdim, q_scale, y, nq, bonus, stream
 // 2 * WARPS half warps of ROWS rows each cover `dim` rows
 #define QF_SCAN_CASE(WARPS, ROWS) \
     if (dim <= 2 * WARPS * ROWS)  \
-        return is_bf16 ? launch_scan<bf16, WARPS, ROWS>(QF_SCAN_ARGS) : launch_scan<float, WARPS, ROWS>(QF_SCAN_ARGS);
+        return is_bf16 ? launch_scan<bf16, WARPS, ROWS, MODE>(QF_SCAN_ARGS) : launch_scan<float, WARPS, ROWS, MODE>(QF_SCAN_ARGS);
 
 // q, k: [T][groups * dim] with row strides; v: [T][heads * vdim]; decay, take: float32 [T][heads]; y: float32 [T][heads * vdim];
 // nq: float32 [T][heads] or null (then n_offset < 0). State pieces: S [heads][dim][vdim] at s_offset, n [heads][dim] at n_offset.
@@ -301,11 +346,144 @@ QF_EXPORT int qf_outer_state_scan(int is_bf16, const void* q, int q_stride, cons
                                   cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (dim <= 0 || vdim <= 0 || n_groups <= 0 || n_heads % n_groups || (n_offset >= 0 && !nq)) return (int)cudaErrorInvalidValue;
+    constexpr int MODE = 0;
+    const float* bonus = nullptr;
     QF_SCAN_CASE(4, 4)
     QF_SCAN_CASE(8, 4)
     QF_SCAN_CASE(16, 4)
     QF_SCAN_CASE(16, 8)
     return (int)cudaErrorInvalidValue;
+}
+
+template <int MODE>
+static int scan_rows(int is_bf16, const void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride,
+                     const float* decay, const int* cu_q, const int* slots, int n_seqs, float* state, long long slot_stride,
+                     long long s_offset, int n_heads, int n_groups, int dim, int vdim, float q_scale, float* y, const float* bonus,
+                     cudaStream_t stream) {
+    const float* take = nullptr;
+    float* nq = nullptr;
+    const long long n_offset = -1;
+    QF_SCAN_CASE(4, 4)
+    QF_SCAN_CASE(8, 4)
+    QF_SCAN_CASE(16, 4)
+    QF_SCAN_CASE(16, 8)
+    return (int)cudaErrorInvalidValue;
+}
+
+// The scan with a decay per row of S: decay is float32 [T][heads * dim]; `bonus` null: the output is read after the token's
+// update (MODE 1); `bonus` float32 [heads][dim]: before it, the token's own outer product entering under the bonus (MODE 2).
+QF_EXPORT int qf_outer_state_scan_rows(int is_bf16, const void* q, int q_stride, const void* k, int k_stride, const void* v,
+                                       int v_stride, const float* decay, const int* cu_q, const int* slots, int n_seqs,
+                                       float* state, long long slot_stride, long long s_offset, int n_heads, int n_groups, int dim,
+                                       int vdim, float q_scale, float* y, const float* bonus, cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (dim <= 0 || vdim <= 0 || n_groups <= 0 || n_heads % n_groups || !decay) return (int)cudaErrorInvalidValue;
+    if (bonus)
+        return scan_rows<2>(is_bf16, q, q_stride, k, k_stride, v, v_stride, decay, cu_q, slots, n_seqs, state, slot_stride, s_offset,
+                            n_heads, n_groups, dim, vdim, q_scale, y, bonus, stream);
+    return scan_rows<1>(is_bf16, q, q_stride, k, k_stride, v, v_stride, decay, cu_q, slots, n_seqs, state, slot_stride, s_offset,
+                        n_heads, n_groups, dim, vdim, q_scale, y, bonus, stream);
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// A decay per channel from its pre-activation, float32 in and out:
+//   kind 0:  w = exp(-exp(z + b))                 (a decay that a low-rank product and a learned offset set)
+//   kind 1:  w = sigmoid(z + b)^(1 / tau) = exp(logsigmoid(z + b) * inv_tau)
+__global__ void __launch_bounds__(256)
+channel_decay_kernel(const float* __restrict__ pre, int stride, const float* __restrict__ bias, int channels, size_t total, int kind,
+                     float inv_tau, float* __restrict__ out) {
+    grid_chain_entry();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / channels;
+        const int c = (int)(i % channels);
+        const float z = pre[t * stride + c] + (bias ? bias[c] : 0.f);
+        out[i] = kind == 0 ? expf(-expf(z)) : expf(log_sigmoid(z) * inv_tau);
+    }
+}
+
+QF_EXPORT int qf_channel_decay(const float* pre, int stride, const float* bias, int n_tokens, int channels, int kind, float inv_tau,
+                               float* out, cudaStream_t stream) {
+    const size_t total = (size_t)n_tokens * channels;
+    if (total == 0) return 0;
+    if (kind < 0 || kind > 1) return (int)cudaErrorInvalidValue;
+    const size_t most = (size_t)(qf_sm_count() > 0 ? qf_sm_count() : 1) * 16, want = (total + 255) / 256;
+    return (int)launch_pdl(channel_decay_kernel, dim3((unsigned)(want < most ? want : most)), dim3(256), 0, stream, pre, stride, bias,
+                           channels, total, kind, inv_tau, out);
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Token shift into several mixes at once: with h' the row of the token before (the sequence's kept row for its first token
+// of the step, zeros at its start), mix s of token t is  h_t + (h'_t - h_t) * mu[s]  (float32 inside), written to
+// out[t][s * width ..]. The kept row (float32 [width] at `offset` of the slot's state) then takes the sequence's last h.
+// In a step of one token per sequence (`single`) the thread that read a kept element also replaces it; otherwise a second
+// kernel does, after every block of the first has read.
+template <typename T>
+__global__ void __launch_bounds__(256)
+shift_mix_kernel(const T* __restrict__ h, int h_stride, const float* __restrict__ mu, int n_mixes, const int* __restrict__ cu_q,
+                 const int* __restrict__ tok_seq, const int* __restrict__ slots, float* __restrict__ state, long long slot_stride,
+                 long long offset, int width, size_t total, T* __restrict__ out, int single) {
+    grid_chain_entry();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / width;
+        const int c = (int)(i % width);
+        const int seq = tok_seq[t], at = (int)t - cu_q[seq];
+        const float mine = Num<T>::to_f(h[t * h_stride + c]);
+        float before = 0.f;
+        if (at > 0) {
+            before = Num<T>::to_f(h[(t - 1) * h_stride + c]);
+        } else {
+            const int slot = slots[seq];
+            if (slot >= 0) {
+                float* kept = state + slot * slot_stride + offset + c;
+                before = *kept;
+                if (single) *kept = mine;
+            }
+        }
+        const float diff = before - mine;
+        for (int s = 0; s < n_mixes; ++s)
+            out[t * ((size_t)n_mixes * width) + (size_t)s * width + c] = Num<T>::from_f(fmaf(diff, mu[(size_t)s * width + c], mine));
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+shift_keep_kernel(const T* __restrict__ h, int h_stride, const int* __restrict__ cu_q, const int* __restrict__ slots, int n_seqs,
+                  float* __restrict__ state, long long slot_stride, long long offset, int width) {
+    grid_chain_entry();
+    const size_t total = (size_t)n_seqs * width;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int seq = (int)(i / width), c = (int)(i % width);
+        const int slot = slots[seq], end = cu_q[seq + 1];
+        if (slot < 0 || end <= cu_q[seq]) continue;
+        state[slot * slot_stride + offset + c] = Num<T>::to_f(h[(size_t)(end - 1) * h_stride + c]);
+    }
+}
+
+template <typename T>
+static int launch_shift_mix(const void* h, int h_stride, const float* mu, int n_mixes, const int* cu_q, const int* tok_seq,
+                            const int* slots, int n_seqs, float* state, long long slot_stride, long long offset, int n_tokens,
+                            int width, void* out, int single, cudaStream_t stream) {
+    const size_t total = (size_t)n_tokens * width, most = (size_t)(qf_sm_count() > 0 ? qf_sm_count() : 1) * 16;
+    size_t want = (total + 255) / 256;
+    int code = (int)launch_pdl(shift_mix_kernel<T>, dim3((unsigned)(want < most ? want : most)), dim3(256), 0, stream, (const T*)h,
+                               h_stride, mu, n_mixes, cu_q, tok_seq, slots, state, slot_stride, offset, width, total, (T*)out, single);
+    if (code || single) return code;
+    want = ((size_t)n_seqs * width + 255) / 256;
+    return (int)launch_pdl(shift_keep_kernel<T>, dim3((unsigned)(want < most ? want : most)), dim3(256), 0, stream, (const T*)h,
+                           h_stride, cu_q, slots, n_seqs, state, slot_stride, offset, width);
+}
+
+// h: [T][width] with a row stride; mu: float32 [n_mixes][width]; out: [T][n_mixes * width]; state float32 rows per slot.
+// single: 1 only if every sequence of the step brings exactly one token.
+QF_EXPORT int qf_shift_mix(int is_bf16, const void* h, int h_stride, const float* mu, int n_mixes, const int* cu_q,
+                           const int* tok_seq, const int* slots, int n_seqs, float* state, long long slot_stride, long long offset,
+                           int n_tokens, int width, void* out, int single, cudaStream_t stream) {
+    if (n_tokens <= 0 || n_seqs <= 0) return 0;
+    if (n_mixes <= 0 || width <= 0) return (int)cudaErrorInvalidValue;
+    return is_bf16 ? launch_shift_mix<bf16>(h, h_stride, mu, n_mixes, cu_q, tok_seq, slots, n_seqs, state, slot_stride, offset, n_tokens,
+                                            width, out, single, stream)
+                   : launch_shift_mix<float>(h, h_stride, mu, n_mixes, cu_q, tok_seq, slots, n_seqs, state, slot_stride, offset,
+                                             n_tokens, width, out, single, stream);
 }
 
 // ------------------------------------------------------------------------------------------------------------------

@@ -1312,13 +1312,23 @@ def moe_tile_rows(n_tokens: int, n_experts: int, top: int, weight: torch.Tensor)
 
 def moe_plan(logits: Optional[torch.Tensor], top: int, softmax_scores: bool = False, renormalize: bool = False,
              tile_rows: int = GROUP_TILE_ROWS, x: Optional[torch.Tensor] = None, router: Optional[torch.Tensor] = None,
-             bias: Optional[torch.Tensor] = None) -> MoePlan:
+             bias: Optional[torch.Tensor] = None, correction: Optional[torch.Tensor] = None, groups=None) -> MoePlan:
     """Route: logits float32 [T, E] -> the `top` experts with the largest scores per token (sigmoid of the logit, or the
     softmax over the experts) and the sorted rows (see `MoePlan`), cut into tiles of `tile_rows`. Everything stays on the
     device. With `logits` None, the kernel makes the logits itself from `x` [T, W] and `router` [E, W] (float32 sums; for
-    steps of few tokens, T * E <= MOE_FUSED_ROUTER_MAX). `bias` (float32 [E]) is added to the logits before the choice."""
+    steps of few tokens, T * E <= MOE_FUSED_ROUTER_MAX). `bias` (float32 [E]) is added to the logits before the choice.
+    `correction` (float32 [E]) and `groups` = (count, keep), with sigmoid scores: the choice goes by score + correction, and
+    only among the experts of the `keep` best of `count` equal groups of neighbouring experts, a group's score being the sum
+    of its two largest choice scores; the weights are the scores without the correction."""
     if bias is not None:
         _dev("bias", bias, torch.float32)
+    group_count, group_keep = (0, 0)
+    if correction is not None or groups is not None:
+        group_count, group_keep = (int(groups[0]), int(groups[1])) if groups is not None else (1, 1)
+        if softmax_scores:
+            raise KernelError("moe_plan: a correction or groups go with sigmoid scores")
+        if correction is not None:
+            _dev("correction", correction, torch.float32)
     if logits is not None:
         _dev("logits", logits, torch.float32)
         n_tokens, n_experts = logits.shape
@@ -1331,24 +1341,30 @@ def moe_plan(logits: Optional[torch.Tensor], top: int, softmax_scores: bool = Fa
             raise KernelError("moe_plan: x [T, W] and router [E, W] with T * E <= %d, or give the logits" % MOE_FUSED_ROUTER_MAX)
     if bias is not None and bias.numel() != n_experts:
         raise KernelError("moe_plan: bias must hold one float32 per expert")
+    if correction is not None and correction.numel() != n_experts:
+        raise KernelError("moe_plan: correction must hold one float32 per expert")
+    if group_count and (not 1 <= group_keep <= group_count <= 64 or n_experts % group_count or group_keep * (n_experts // group_count) < top):
+        raise KernelError(f"moe_plan: {group_keep} of {group_count} groups over {n_experts} experts cannot yield {top} choices "
+                          "(up to 64 equal groups)")
     plan = MoePlan(n_tokens, n_experts, top, (logits if logits is not None else x).device, tile_rows)
     if logits is not None and n_tokens >= MOE_LONG_PLAN_TOKENS and n_experts <= 4096:
         expert_rows = torch.zeros(n_experts, dtype=torch.int32, device=logits.device)
-        code = library("moe").qf_moe_plan_long_biased(
+        code = library("moe").qf_moe_plan_long_grouped(
             _ptr(logits), _I(n_tokens), _I(n_experts), _I(top), _I(int(softmax_scores)), _I(int(renormalize)),
             _ptr(plan.pair_expert), _ptr(plan.pair_weight), _ptr(plan.sorted_token), _ptr(plan.sorted_weight), _ptr(plan.dest),
             _ptr(plan.offsets), _ptr(plan.tile_group), _ptr(plan.tile_row0), _ptr(plan.n_tiles), _I(plan.max_tiles),
-            _I(tile_rows), _ptr(expert_rows), _ptr(bias), _stream())
+            _I(tile_rows), _ptr(expert_rows), _ptr(bias), _ptr(correction), _I(group_count), _I(group_keep), _stream())
         if code == 1:
             raise KernelError(f"moe_plan: {top} of {n_experts} experts is not supported (top <= 16)")
         _check(code, "moe_plan")
         return plan
-    code = library("moe").qf_moe_plan_biased(_ptr(logits), _I(n_tokens), _I(n_experts), _I(top), _I(int(softmax_scores)),
+    code = library("moe").qf_moe_plan_grouped(_ptr(logits), _I(n_tokens), _I(n_experts), _I(top), _I(int(softmax_scores)),
                                       _I(int(renormalize)), _ptr(plan.pair_expert), _ptr(plan.pair_weight),
                                       _ptr(plan.sorted_token), _ptr(plan.sorted_weight), _ptr(plan.dest), _ptr(plan.offsets),
                                       _ptr(plan.tile_group), _ptr(plan.tile_row0), _ptr(plan.n_tiles), _I(plan.max_tiles),
                                       _I(tile_rows), _ptr(x if logits is None else None), _ptr(router if logits is None else None),
-                                      _I(width), _I(_is_bf16(x.dtype) if logits is None else 0), _ptr(bias), _stream())
+                                      _I(width), _I(_is_bf16(x.dtype) if logits is None else 0), _ptr(bias), _ptr(correction),
+                                      _I(group_count), _I(group_keep), _stream())
     if code == 1:
         raise KernelError(f"moe_plan: {top} of {n_experts} experts is not supported (top <= 16, experts <= 8192)")
     _check(code, "moe_plan")
@@ -1500,11 +1516,11 @@ def tc_gemm_grouped(epilogue: int, x: torch.Tensor, weight: torch.Tensor, plan: 
 
 # ---------------------------------------------------------------------------------------------------------------------
 # Elementwise kernels of feed-forwards with a bias and of capped logits (csrc/activation.cu)
-ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2, "relu": 3, "gelu": 4}
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2, "relu": 3, "gelu": 4, "tanh": 5}
 
 
 def bias_act(x: torch.Tensor, bias: Optional[torch.Tensor], kind: str, out: torch.Tensor) -> None:
-    """out = act(x + bias), float32 inside. kind: relu2 (the square of relu), gelu_tanh, gelu (the exact form, through erf), silu, relu."""
+    """out = act(x + bias), float32 inside. kind: relu2 (the square of relu), gelu_tanh, gelu (the exact form, through erf), silu, relu, tanh."""
     _dev("x", x)
     _dev("out", out, x.dtype)
     if kind not in ACTIVATIONS:
@@ -1706,3 +1722,163 @@ def causal_conv_silu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch
 def causal_conv(x, weight, bias, cu_q, tok_seq, slots, state, offset, out, single: bool = False) -> None:
     """`causal_conv_silu` without the activation."""
     causal_conv_silu(x, weight, bias, cu_q, tok_seq, slots, state, offset, out, activation="none", single=single)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Outputs that enter the stream under a factor each; norms over runs of columns; rows drawn towards another layer's
+# (csrc/norm.cu)
+def add_rms_norm_scaled(hidden: torch.Tensor, a: torch.Tensor, scale_a: float, b: Optional[torch.Tensor], scale_b: float,
+                        weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """hidden += scale_a * a + scale_b * b (b may be None), float32; out = rmsnorm(hidden) * weight. hidden float32 [R, W]; a, b,
+    weight and out share the activation dtype."""
+    _dev("hidden", hidden, torch.float32)
+    _dev("weight", weight)
+    _dev("out", out, weight.dtype)
+    rows, width = hidden.shape
+    if weight.shape != (width,) or out.shape != hidden.shape:
+        raise KernelError("add_rms_norm_scaled: shapes of weight/out do not match hidden")
+    for name, t in (("a", a), ("b", b)):
+        if t is not None:
+            _dev(name, t, weight.dtype)
+            if t.shape != hidden.shape:
+                raise KernelError(f"add_rms_norm_scaled: {name} and hidden differ in shape")
+    if a is None:
+        raise KernelError("add_rms_norm_scaled: the first output is required")
+    _check(library("norm").qf_add_scaled_rms_norm(_I(_is_bf16(weight.dtype)), _ptr(hidden), _ptr(a), _F(scale_a), _ptr(b), _F(scale_b),
+                                                  _ptr(weight), _ptr(out), _I(rows), _I(width), _F(eps), _stream()), "add_rms_norm_scaled")
+
+
+def residual_add_scaled(hidden: torch.Tensor, a: torch.Tensor, scale_a: float, b: Optional[torch.Tensor] = None,
+                        scale_b: float = 0.0) -> None:
+    """hidden (float32) += scale_a * a + scale_b * b, in place; b may be None."""
+    _dev("hidden", hidden, torch.float32)
+    _dev("a", a)
+    if a.shape != hidden.shape or (b is not None and (b.shape != hidden.shape or b.dtype != a.dtype)):
+        raise KernelError("residual_add_scaled: shapes or dtypes differ")
+    if b is not None:
+        _dev("b", b, a.dtype)
+    _check(library("norm").qf_residual_add_scaled(_I(_is_bf16(a.dtype)), _ptr(hidden), _ptr(a), _F(scale_a), _ptr(b), _F(scale_b),
+                                                  _LL(hidden.numel()), _stream()), "residual_add_scaled")
+
+
+def rms_norm_cols(x: torch.Tensor, runs, eps: float) -> None:
+    """RMS norms over runs of columns of x [T, C] (rows may be strided), in place, float32 inside. `runs`: one or two of
+    (first column, width, count, weight [width]): x[:, c0:c0 + width] <- x / sqrt(sum(x^2) / count + eps) * weight; `count` is
+    how many of the run's columns carry numbers (columns of padding hold zeros)."""
+    _rows("x", x)
+    _is_bf16(x.dtype)
+    runs = list(runs)
+    if not 1 <= len(runs) <= 2:
+        raise KernelError("rms_norm_cols: one or two runs of columns")
+    flat = []
+    for col0, width, count, weight in runs:
+        _dev("weight", weight, x.dtype)
+        if col0 < 0 or width <= 0 or col0 + width > x.shape[1] or weight.numel() != width or not 0 < count <= width:
+            raise KernelError("rms_norm_cols: a run must lie within the row, with one weight per column")
+        flat += [_I(col0), _I(width), _I(count), _ptr(weight)]
+    if len(runs) == 1:
+        flat += [_I(0), _I(0), _I(0), _P(0)]
+    _check(library("norm").qf_rms_norm_cols(_I(_is_bf16(x.dtype)), _ptr(x), _I(x.stride(0)), _I(x.shape[0]), _I(len(runs)), *flat,
+                                            _F(eps), _stream()), "rms_norm_cols")
+
+
+def mix_rows(x: torch.Tensor, other: torch.Tensor, heads: int, size: int, x_head: int, other_head: int, weight: float) -> None:
+    """x[t, h * x_head + c] <- (1 - weight) * x[...] + weight * other[t, h * other_head + c] for c < size, in place, float32
+    inside; x and other: [T, >= heads * head] views with unit inner stride, of one dtype."""
+    _rows("x", x)
+    _rows("other", other, x.dtype)
+    _is_bf16(x.dtype)
+    if x.shape[0] != other.shape[0] or size > min(x_head, other_head) or (heads - 1) * x_head + size > x.shape[1] \
+            or (heads - 1) * other_head + size > other.shape[1]:
+        raise KernelError("mix_rows: the heads do not fit the rows")
+    _check(library("norm").qf_mix_rows(_I(_is_bf16(x.dtype)), _ptr(x), _I(x.stride(0)), _ptr(other), _I(other.stride(0)), _I(x.shape[0]),
+                                       _I(heads), _I(size), _I(x_head), _I(other_head), _F(weight), _stream()), "mix_rows")
+
+
+def bias_glu(gate_up: torch.Tensor, bias: Optional[torch.Tensor], kind: str, out: torch.Tensor) -> None:
+    """out = act(gate + bias[:I]) * (up + bias[I:]) from the fused product gate_up [T, 2 I] (gate columns first); float32
+    inside; bias [2 I] or None; kind as in `bias_act`."""
+    _dev("gate_up", gate_up)
+    _dev("out", out, gate_up.dtype)
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"bias_glu: unknown activation {kind!r}; known: {', '.join(ACTIVATIONS)}")
+    rows, inter = out.shape
+    if gate_up.shape != (rows, 2 * inter):
+        raise KernelError("bias_glu: gate_up must be [rows, 2 * width of out]")
+    if bias is not None:
+        _dev("bias", bias, gate_up.dtype)
+        if bias.numel() != 2 * inter:
+            raise KernelError("bias_glu: bias must hold one element per column of gate_up")
+    _check(library("activation").qf_bias_glu(_I(_is_bf16(gate_up.dtype)), _ptr(gate_up), _ptr(bias), _ptr(out), _I(rows), _I(inter),
+                                             _I(ACTIVATIONS[kind]), _stream()), "bias_glu")
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Recurrences with a decay per row of the state (csrc/recurrent.cu)
+def shift_mix(h: torch.Tensor, mu: torch.Tensor, cu_q: torch.Tensor, tok_seq: torch.Tensor, slots: torch.Tensor,
+              state: torch.Tensor, offset: int, out: torch.Tensor, single: bool = False) -> None:
+    """Token shift into several mixes: out[t, s * W:(s + 1) * W] = h_t + (h_(t-1) - h_t) * mu[s], float32 inside, h before a
+    sequence's first token of the step being its kept row (float32 [W] at `offset` of the slot's state; zeros at a sequence's
+    start), which then takes the sequence's last h. h: [T, W] (rows may be strided); mu: float32 [S, W]; out [T, S * W].
+    `single`: the caller's promise that every sequence of the step brings exactly one token."""
+    _rows("h", h)
+    _dev("out", out, h.dtype)
+    _dev("mu", mu, torch.float32)
+    _is_bf16(h.dtype)
+    n, width = h.shape
+    if mu.dim() != 2 or mu.shape[1] != width or out.shape != (n, mu.shape[0] * width):
+        raise KernelError("shift_mix: mu must be float32 [mixes, width], out [T, mixes * width]")
+    _state(state, (offset, width))
+    n_seqs = cu_q.numel() - 1
+    _check(library("recurrent").qf_shift_mix(_I(_is_bf16(h.dtype)), _ptr(h), _I(h.stride(0)), _ptr(mu), _I(mu.shape[0]), _ptr(cu_q),
+                                             _ptr(tok_seq), _ptr(slots), _I(n_seqs), _ptr(state), _LL(state.stride(0)), _LL(offset),
+                                             _I(n), _I(width), _ptr(out), _I(1 if single and n == n_seqs else 0), _stream()), "shift_mix")
+
+
+DECAYS = {"double_exp": 0, "sigmoid_root": 1}
+
+
+def channel_decay(pre: torch.Tensor, bias: Optional[torch.Tensor], kind: str, out: torch.Tensor, tau: float = 1.0) -> None:
+    """A decay per channel from float32 pre-activations [T, C] (rows may be strided) and a float32 bias [C]:
+    "double_exp": exp(-exp(pre + bias));  "sigmoid_root": sigmoid(pre + bias)^(1 / tau). out float32 [T, C]."""
+    _rows("pre", pre, torch.float32)
+    _dev("out", out, torch.float32)
+    if kind not in DECAYS or out.shape != pre.shape or tau <= 0:
+        raise KernelError("channel_decay: kind is 'double_exp' or 'sigmoid_root', out has pre's shape, tau is positive")
+    if bias is not None:
+        _dev("bias", bias, torch.float32)
+        if bias.numel() != pre.shape[1]:
+            raise KernelError("channel_decay: bias must hold one float32 per channel")
+    _check(library("recurrent").qf_channel_decay(_ptr(pre), _I(pre.stride(0)), _ptr(bias), _I(pre.shape[0]), _I(pre.shape[1]),
+                                                 _I(DECAYS[kind]), _F(1.0 / tau), _ptr(out), _stream()), "channel_decay")
+
+
+def outer_state_scan_rows(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, cu_q: torch.Tensor,
+                          slots: torch.Tensor, state: torch.Tensor, s_offset: int, n_heads: int, dim: int, vdim: int,
+                          q_scale: float, y: torch.Tensor, bonus: Optional[torch.Tensor] = None) -> None:
+    """The recurrence of a matrix state per head with a decay per row of the state, float32 inside:
+        S <- diag(decay_t) S + k_t v_t^T,   y_t = S^T (q_scale q_t)                         (bonus None: read after the update)
+        y_t = (S + diag(bonus) k_t v_t^T)^T (q_scale q_t),  then the same update            (bonus float32 [heads, dim])
+    q, k: [T, heads * dim], v: [T, heads * vdim] in the activation dtype (rows may be strided); decay float32 [T, heads * dim];
+    y float32 [T, heads * vdim]; S in `state` at s_offset as [heads, dim, vdim]."""
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        _rows(name, t, q.dtype)
+    _is_bf16(q.dtype)
+    n = q.shape[0]
+    if q.shape[1] != n_heads * dim or k.shape != q.shape or v.shape != (n, n_heads * vdim):
+        raise KernelError("outer_state_scan_rows: q, k must be [T, heads * dim], v [T, heads * vdim]")
+    if dim > OUTER_STATE_MAX_DIM:
+        raise KernelError(f"outer_state_scan_rows: a state of {dim} rows per head exceeds the kernel's {OUTER_STATE_MAX_DIM}")
+    _dev("decay", decay, torch.float32)
+    _dev("y", y, torch.float32)
+    if decay.shape != (n, n_heads * dim) or y.shape != (n, n_heads * vdim):
+        raise KernelError("outer_state_scan_rows: decay must be float32 [T, heads * dim], y float32 [T, heads * vdim]")
+    if bonus is not None:
+        _dev("bonus", bonus, torch.float32)
+        if bonus.numel() != n_heads * dim:
+            raise KernelError("outer_state_scan_rows: bonus must be float32 [heads, dim]")
+    _state(state, (s_offset, n_heads * dim * vdim))
+    _check(library("recurrent").qf_outer_state_scan_rows(
+        _I(_is_bf16(q.dtype)), _ptr(q), _I(q.stride(0)), _ptr(k), _I(k.stride(0)), _ptr(v), _I(v.stride(0)), _ptr(decay), _ptr(cu_q),
+        _ptr(slots), _I(cu_q.numel() - 1), _ptr(state), _LL(state.stride(0)), _LL(s_offset), _I(n_heads), _I(n_heads), _I(dim),
+        _I(vdim), _F(q_scale), _ptr(y), _ptr(bonus), _stream()), "outer_state_scan_rows")

@@ -31,6 +31,12 @@ Options that other designs switch on, each a parameter of the spec (all off for 
                  keys and values as the cache holds them, in the same softmax. They live in a second paged cache of one row
                  per block; the positions themselves stay until their block is complete
   head_gate      every head's output is multiplied by sigmoid(G h)_head, one more projection [heads, hidden] of the same input
+  row_norm_eps   q and k are RMS-normed over their WHOLE rows (all heads at once: the mean over heads * head_dim numbers),
+                 after the biases and before the rotation, with a weight per column (`q_row_norm` [heads * head_dim],
+                 `k_row_norm` [kv_heads * head_dim])
+  value_mix      {"role": "source" | "mix", "key": name}: the layers that share a key form a chain through one step. The
+                 source keeps its values (after the bias) for the others; a "mix" layer replaces its own by
+                 (1 - l) v + l v_source of the same token, l a learned number (`value_mix`), and caches the mixed values
 The position part may pair components 2j and 2j + 1 (`rotary_interleaved`) instead of j and j + R/2.
 """
 from __future__ import annotations
@@ -74,6 +80,13 @@ class GqaAttention(Mixer):
         self.qk_norm_eps = None if p.get("qk_norm_eps") is None else float(p["qk_norm_eps"])
         self.pool = int(p.get("pool") or 0)
         self.gated = bool(p.get("head_gate", False))
+        self.row_norm_eps = None if p.get("row_norm_eps") is None else float(p["row_norm_eps"])
+        self.value_mix = dict(p["value_mix"]) if p.get("value_mix") else None
+        if self.value_mix is not None and (self.value_mix.get("role") not in ("source", "mix") or not p.get("own_kv", True)):
+            raise ValueError("gqa_attention: value_mix has the role 'source' or 'mix' and goes with values of the layer's own")
+        if self.row_norm_eps is not None and (p.get("qk_norm_eps") is not None or int(p.get("conv_taps") or 0) > 0 or not p.get("own_kv", True)):
+            raise ValueError("gqa_attention: a norm over whole rows goes with keys of the layer's own, without a norm per head "
+                             "before the rotation and without a short convolution")
         if self.sink not in ("none", "unit", "learned"):
             raise ValueError(f"gqa_attention: sink {self.sink!r} is not known ('none', 'unit' or 'learned')")
         if self.unit_norm_eps is not None and self.qk_norm_eps is not None:
@@ -87,7 +100,8 @@ class GqaAttention(Mixer):
         # the form that every tensor-core kernel and fused product of this part takes
         self.plain = (self.value_dim == self.key_dim and self.unit_norm_eps is None and self.softcap == 0.0 and self.chunk == 0
                       and self.sink == "none" and self.own_kv and self.conv_taps == 0 and self.qk_norm_eps is None
-                      and self.pool == 0 and not self.gated and not self.interleaved)
+                      and self.pool == 0 and not self.gated and not self.interleaved and self.row_norm_eps is None
+                      and self.value_mix is None)
         self.qkv_bias = bool(p.get("qkv_bias", False))
         self.out_bias = bool(p.get("out_bias", False))
         self.scale = float(p.get("scale") or self.key_dim ** -0.5)
@@ -101,7 +115,8 @@ class GqaAttention(Mixer):
         self.kv_width = self.n_kv * self.head_dim
         self.qkv_width = self.q_width + (2 * self.kv_width if self.own_kv else 0)   # the gates' columns follow
         self.qkv_weight = self.qkv_bias_t = self.o_weight = self.o_bias_t = self.sinks = None
-        self.conv_weight = self.q_norm = self.k_norm = None
+        self.conv_weight = self.q_norm = self.k_norm = self.q_row_norm = self.k_row_norm = None
+        self.mix_weight = 0.0
 
     def sub_parts(self):
         return [self.position] if self.position is not None else []
@@ -130,11 +145,16 @@ class GqaAttention(Mixer):
             specs.append(TensorSpec(self.file_name("sink"), (self.n_heads,), init="logit", keep="float32"))
         if self.gated:
             specs.append(TensorSpec(self.file_name("g_weight"), (self.n_heads, self.hidden)))
+        if self.row_norm_eps is not None:
+            specs += [TensorSpec(self.file_name("q_row_norm"), (self.n_heads * kd,), init="norm"),
+                      TensorSpec(self.file_name("k_row_norm"), (self.n_kv * kd,), init="norm")]
+        if self.value_mix is not None and self.value_mix["role"] == "mix":
+            specs.append(TensorSpec(self.file_name("value_mix"), (), init="fraction", keep="float32"))
         return specs
 
     def kernel_libraries(self, dtype):
         libs = {"rope_cache", "attention_generic"} | ({"recurrent"} if self.conv_taps > 0 else set()) \
-            | ({"activation"} if self.gated else set())
+            | ({"activation"} if self.gated else set()) | ({"norm"} if self.row_norm_eps is not None or self.value_mix else set())
         if dtype == torch.float32:
             libs.add("gemm_f32")
         elif not self.plain and self.head_dim in ops.FAST_ATTENTION_HEAD_DIMS:
@@ -181,6 +201,11 @@ class GqaAttention(Mixer):
                                           self._padded(t("v_conv"), self.n_kv, vd)), dim=0).to(torch.float32).contiguous()
         if self.qk_norm_eps is not None:
             self.q_norm, self.k_norm = t("q_norm").contiguous(), t("k_norm").contiguous()
+        if self.row_norm_eps is not None:   # (zero weights under the padding, where the rows hold zeros anyway)
+            self.q_row_norm = self._padded(t("q_row_norm"), self.n_heads, kd).contiguous()
+            self.k_row_norm = self._padded(t("k_row_norm"), self.n_kv, kd).contiguous()
+        if self.value_mix is not None and self.value_mix["role"] == "mix":
+            self.mix_weight = float(t("value_mix").float().item())   # a scalar, read once when the weights are bound
         if self.qkv_bias:
             pieces = [self._padded(t("q_bias"), self.n_heads, kd)]
             if self.own_kv:
@@ -199,7 +224,7 @@ class GqaAttention(Mixer):
 
     def step_weights(self):
         return [t for t in (self.qkv_weight, self.qkv_bias_t, self.o_weight, self.o_bias_t, self.conv_weight, self.q_norm,
-                            self.k_norm) if t is not None]
+                            self.k_norm, self.q_row_norm, self.k_row_norm) if t is not None]
 
     def forward(self, x, ctx, site, writes_cache):
         n = x.shape[0]
@@ -255,7 +280,18 @@ class GqaAttention(Mixer):
             raise ValueError("gqa_attention: a layer with a convolution's state or pooled rows cannot read another entry's cache")
         kv_site = site["kv"] if bundled else site
         inv_freq, rot_dim = self.position.fused_rotary() if self.position is not None else (None, 0)
-        qkv = ops.linear_rows(x, self.qkv_weight)           # [T, q | k | v (| gates)]
+        late_bias = self.qkv_bias_t
+        if self.row_norm_eps is not None or self.value_mix is not None:
+            # what follows reads q, k and v with their biases: the bias joins the product, not the rotation kernel
+            qkv = ops.linear(x, self.qkv_weight, self.qkv_bias_t) if self.qkv_bias_t is not None else ops.linear_rows(x, self.qkv_weight)
+            late_bias = None
+            if self.row_norm_eps is not None:
+                ops.rms_norm_cols(qkv, ((0, self.q_width, self.n_heads * self.key_dim, self.q_row_norm),
+                                        (self.q_width, self.kv_width, self.n_kv * self.key_dim, self.k_row_norm)), self.row_norm_eps)
+            if self.value_mix is not None:
+                self._mix_values(qkv, ctx)
+        else:
+            qkv = ops.linear_rows(x, self.qkv_weight)           # [T, q | k | v (| gates)]
         gates = qkv[:, self.qkv_width:self.qkv_width + self.n_heads] if self.gated else None
         if self.conv_taps > 0:
             mixed = torch.empty((n, self.qkv_width), dtype=x.dtype, device=x.device)
@@ -266,7 +302,7 @@ class GqaAttention(Mixer):
         args = ops.KvSiteArgs(kv_site.storage, kv_site.table, self.n_kv, self.head_dim)
         norm_first = self.qk_norm_eps is not None
         ops.rope_cache_write(qkv, ctx.tok_seq, ctx.tok_pos, ctx.slots, inv_freq, rot_dim, self.n_heads, q, args, writes_cache,
-                             ctx.err, bias=self.qkv_bias_t, unit_norm_eps=self.qk_norm_eps if norm_first else self.unit_norm_eps,
+                             ctx.err, bias=late_bias, unit_norm_eps=self.qk_norm_eps if norm_first else self.unit_norm_eps,
                              norm_dim=self.key_dim, has_kv=self.own_kv, interleaved=self.interleaved, norm_first=norm_first,
                              q_norm=self.q_norm, k_norm=self.k_norm)
         blocks = None
@@ -293,6 +329,22 @@ class GqaAttention(Mixer):
         if self.gated:
             ops.head_gate(attended, gates, self.n_heads)
         return ops.linear(attended, self.o_weight, self.o_bias_t) if self.o_bias_t is not None else ops.linear_rows(attended, self.o_weight)
+
+    def _mix_values(self, qkv, ctx) -> None:
+        """The chain of layers that share values through one step: the source leaves its values (a view of its projection's
+        output, kept alive by the step's memo) for the layers after it; a mixing layer draws its own towards them in place."""
+        key = ("gqa_attention.value_mix", self.value_mix["key"])
+        memo = ctx.step_memo if ctx.step_memo is not None else {}
+        values = qkv[:, self.q_width + self.kv_width:self.q_width + 2 * self.kv_width]
+        if self.value_mix["role"] == "source":
+            memo[key] = (values, self.n_kv, self.value_dim, self.head_dim)
+            return
+        if key not in memo:
+            raise RuntimeError("gqa_attention: a layer mixes in the values of a layer that has not run in this step")
+        source, heads, size, source_head = memo[key]
+        if (heads, size) != (self.n_kv, self.value_dim):
+            raise ValueError("gqa_attention: layers that mix their values have as many key/value heads of the same value size")
+        ops.mix_rows(values, source, self.n_kv, self.value_dim, self.head_dim, source_head, self.mix_weight)
 
     # ---- the form for decode steps of up to 64 sequences that works on the residual stream in place: the norm, bias,
     # rotation and cache write ride on the QKV product and the addition on the output projection wherever a kernel of

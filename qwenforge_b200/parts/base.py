@@ -44,7 +44,9 @@ class TensorSpec:
     """One tensor of the weight files.
 
     init  how the random-weights mode draws it: "matrix" N(0, 0.02), "bias" N(0, 0.02), "norm" 1 + N(0, 0.1),
-          "logit" N(0, 1), "conv" (1 + N(0, 0.5)) / sqrt(taps), "fraction" sigmoid(N(0, 1))
+          "logit" N(0, 1), "conv" (1 + N(0, 0.5)) / sqrt(taps), "fraction" sigmoid(N(0, 1)), "rate" N(-1, 1),
+          "low_rank" N(0, 0.5)
+    shape an extent of -1 takes whatever size the file holds (the part reads it from the tensor it is bound to)
     keep  "compute": kept in the activation dtype (bfloat16, or float32 on the 32-bit path)
           "stored":  kept as the file stores it if that is a 32-bit float, else as "compute"
           "int32":   an integer table, kept as int32
@@ -121,6 +123,30 @@ class PendingPair(Pending):
     def value(self) -> torch.Tensor:
         parts = [t.to(torch.float32) for t in (self.a, self.b) if t is not None]
         return parts[0] + parts[1] if len(parts) == 2 else parts[0]
+
+
+class PendingScaled(Pending):
+    """One or two sublayer outputs that enter the stream under a factor each: hidden += scale_a * a + scale_b * b (float32).
+    What a block with a residual multiplier leaves pending, and what two mixers that run side by side hand to their block."""
+    __slots__ = ("a", "scale_a", "b", "scale_b")
+
+    def __init__(self, a, scale_a: float, b=None, scale_b: float = 0.0):
+        self.a, self.scale_a, self.b, self.scale_b = a, float(scale_a), b, float(scale_b)
+
+    @staticmethod
+    def of(output, factor: float) -> "PendingScaled":
+        """A mixer's or feed-forward's output (a tensor, or already a scaled pair) under one more factor."""
+        if isinstance(output, PendingScaled):
+            return PendingScaled(output.a, output.scale_a * factor, output.b, output.scale_b * factor)
+        return PendingScaled(output, factor)
+
+    def add_to(self, hidden: torch.Tensor) -> None:
+        from .. import ops
+        ops.residual_add_scaled(hidden, self.a, self.scale_a, self.b, self.scale_b)
+
+    def value(self) -> torch.Tensor:
+        out = self.a.to(torch.float32) * self.scale_a
+        return out if self.b is None else out + self.b.to(torch.float32) * self.scale_b
 
 
 class PendingNormed(Pending):

@@ -8,27 +8,48 @@ from __future__ import annotations
 import torch
 
 from ..cache import BundleNeed
-from .base import Norm, Part, PendingNormed, PendingPair
+from .base import Norm, Part, PendingNormed, PendingPair, PendingScaled
 from .registry import build_part, register_part
 
 
 class PreNormBlock(Part):
-    """Reads the layer spec's parts `mixer_norm`, `mixer`, `feed_forward_norm`, `feed_forward`."""
+    """Reads the layer spec's parts `mixer_norm`, `mixer` and, if the layer has a feed-forward, `feed_forward_norm` and
+    `feed_forward`. With the layer spec's parameter `residual_mult` = m every sublayer's output enters the stream times m:
+    h += m * mixer(norm_1(h));  h += m * feed_forward(norm_2(h))  (the product and the sum in float32, inside the next norm's
+    kernel). A mixer may hand back two outputs under a factor each (`PendingScaled`); they go the same way."""
+
+    accepts_pending = (PendingScaled,)
 
     def __init__(self, layer_spec):
         self.kind = "pre_norm"
         self.mixer_norm = build_part("norm", layer_spec.part("mixer_norm"))
         self.mixer = build_part("mixer", layer_spec.part("mixer"))
-        self.feed_forward_norm = build_part("norm", layer_spec.part("feed_forward_norm"))
-        self.feed_forward = build_part("feed_forward", layer_spec.part("feed_forward"))
+        self.feed_forward = self.feed_forward_norm = None
+        if "feed_forward" in layer_spec.parts:
+            self.feed_forward_norm = build_part("norm", layer_spec.part("feed_forward_norm"))
+            self.feed_forward = build_part("feed_forward", layer_spec.part("feed_forward"))
+        self.residual_mult = float(layer_spec.params.get("residual_mult", 1.0))
 
     def sub_parts(self):
-        return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
+        return [p for p in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward) if p is not None]
 
     def cache_need(self):
         return self.mixer.cache_need()
 
+    def _forward_scaled(self, hidden, delta, ctx, site, writes_cache):
+        """The layer with a residual multiplier, a mixer of two outputs, or no feed-forward: every output stays pending
+        with its factor and is added, in float32, by the kernel of the norm that reads the stream next."""
+        x = self.mixer_norm.forward(hidden, delta)
+        delta = PendingScaled.of(self.mixer.forward(x, ctx, site, writes_cache), self.residual_mult)
+        if self.feed_forward is None:
+            return delta
+        x = self.feed_forward_norm.forward(hidden, delta)
+        return PendingScaled.of(self.feed_forward.forward(x, ctx), self.residual_mult)
+
     def forward(self, hidden, delta, ctx, site, writes_cache):
+        if self.residual_mult != 1.0 or self.feed_forward is None or getattr(self.mixer, "scaled_outputs", False) \
+                or isinstance(delta, PendingScaled):
+            return self._forward_scaled(hidden, delta, ctx, site, writes_cache)
         rms = self.mixer_norm.fused_rms()
         if rms is not None and self.mixer.fused_takes(ctx):
             self.mixer.fused_forward(hidden, rms, ctx, site, writes_cache, delta)

@@ -14,6 +14,12 @@ Options, each a parameter of the spec:
                (`limit`, `alpha`) instead of the SwiGLU; the weight is then on the output
   shared       one more expert of the same form with sizes of its own (`size`, `limit`) that every token gets, added to the
                chosen experts' sum; with `gated` it is multiplied by sigmoid(s . h), one number per token
+  gate         "none": the experts have no gate, expert(v) = D_e act(U_e v) with `activation` one of the library's (the square
+               of relu, say); tensors up.<e>, down.<e> only, and the shared expert likewise
+  correction   a float32 number per expert that is added to the sigmoid score for the CHOICE only; the weights are the
+               scores without it
+  groups       (count, keep): the experts form `count` equal groups of neighbours, a group's score is the sum of its two
+               largest choice scores, and only experts of the `keep` best groups can be chosen
 (score "softmax" with `renormalize` is the softmax over the chosen logits alone.)
 
 Routing, sorting by expert and the experts' products all stay on the device (`ops.moe_plan`, `ops.expert_linear`: one
@@ -50,8 +56,20 @@ class RoutedExperts(FeedForward):
         self.router_bias = bool(p.get("router_bias", False))
         self.gate = str(p.get("gate", "swiglu"))
         self.limit, self.alpha = float(p.get("limit") or 0.0), float(p.get("alpha") or 0.0)
-        if self.gate not in ("swiglu", "clamped") or (self.gate == "clamped" and (self.weight_on != "output" or self.limit <= 0)):
-            raise ValueError("routed_experts: gate is 'swiglu' or 'clamped'; the clamped gate takes a positive limit and the weight on the output")
+        if self.gate not in ("swiglu", "clamped", "none") or (self.gate == "clamped" and (self.weight_on != "output" or self.limit <= 0)):
+            raise ValueError("routed_experts: gate is 'swiglu', 'clamped' or 'none'; the clamped gate takes a positive limit and the weight on the output")
+        self.activation = str(p.get("activation") or "relu2")
+        if self.gate == "none" and (self.weight_on != "output" or self.activation not in ops.ACTIVATIONS):
+            raise ValueError("routed_experts: experts without a gate take one of the library's activations and the weight on the output")
+        self.corrected = bool(p.get("correction", False))
+        self.groups = tuple(int(g) for g in p["groups"]) if p.get("groups") else None
+        if (self.corrected or self.groups) and self.score != "sigmoid":
+            raise ValueError("routed_experts: a correction of the choice and groups of experts go with sigmoid scores")
+        if self.groups and (not 1 <= self.groups[1] <= self.groups[0] <= 64 or self.n_experts % self.groups[0]
+                            or self.groups[1] * (self.n_experts // self.groups[0]) < self.top):
+            raise ValueError(f"routed_experts: {self.groups[1]} of {self.groups[0]} groups over {self.n_experts} experts cannot "
+                             f"yield {self.top} choices (up to 64 equal groups)")
+        self.correction = None
         self.shared = dict(p["shared"]) if p.get("shared") else None
         self.router = self.gate_up = self.down = self.bias = None
         self.shared_gate_up = self.shared_down = self.shared_logit = None
@@ -62,15 +80,19 @@ class RoutedExperts(FeedForward):
     def tensor_specs(self):
         specs = [TensorSpec(self.file_name("router"), (self.n_experts, self.hidden))]
         for e in range(self.n_experts):
-            specs += [TensorSpec(self.file_name(f"gate.{e}"), (self.inter, self.hidden)),
-                      TensorSpec(self.file_name(f"up.{e}"), (self.inter, self.hidden)),
+            if self.gate != "none":
+                specs.append(TensorSpec(self.file_name(f"gate.{e}"), (self.inter, self.hidden)))
+            specs += [TensorSpec(self.file_name(f"up.{e}"), (self.inter, self.hidden)),
                       TensorSpec(self.file_name(f"down.{e}"), (self.hidden, self.inter))]
+        if self.corrected:
+            specs.append(TensorSpec(self.file_name("correction"), (self.n_experts,), init="bias", keep="float32"))
         if self.router_bias:
             specs.append(TensorSpec(self.file_name("router_bias"), (self.n_experts,), init="logit", keep="float32"))
         if self.shared is not None:
             size = int(self.shared["size"])
-            specs += [TensorSpec(self.file_name("shared_gate"), (size, self.hidden)), TensorSpec(self.file_name("shared_up"), (size, self.hidden)),
-                      TensorSpec(self.file_name("shared_down"), (self.hidden, size))]
+            if self.gate != "none":
+                specs.append(TensorSpec(self.file_name("shared_gate"), (size, self.hidden)))
+            specs += [TensorSpec(self.file_name("shared_up"), (size, self.hidden)), TensorSpec(self.file_name("shared_down"), (self.hidden, size))]
             if self.shared.get("gated"):
                 specs.append(TensorSpec(self.file_name("shared_logit"), (1, self.hidden)))
         return specs
@@ -81,19 +103,24 @@ class RoutedExperts(FeedForward):
     def bind(self, tensors, dtype, device):
         t = lambda logical: tensors[self.file_name(logical)]
         self.router = t("router")
-        self.gate_up = torch.stack([torch.cat((t(f"gate.{e}"), t(f"up.{e}")), dim=0) for e in range(self.n_experts)]).contiguous()
+        if self.corrected:
+            self.correction = t("correction").to(torch.float32).contiguous()
+        if self.gate == "none":   # (`gate_up` holds the one first product's weights)
+            self.gate_up = torch.stack([t(f"up.{e}") for e in range(self.n_experts)]).contiguous()
+        else:
+            self.gate_up = torch.stack([torch.cat((t(f"gate.{e}"), t(f"up.{e}")), dim=0) for e in range(self.n_experts)]).contiguous()
         self.down = torch.stack([t(f"down.{e}") for e in range(self.n_experts)]).contiguous()
         if self.router_bias:
             self.bias = t("router_bias").to(torch.float32).contiguous()
         if self.shared is not None:
-            self.shared_gate_up = torch.cat((t("shared_gate"), t("shared_up")), dim=0).contiguous()
+            self.shared_gate_up = t("shared_up") if self.gate == "none" else torch.cat((t("shared_gate"), t("shared_up")), dim=0).contiguous()
             self.shared_down = t("shared_down")
             if self.shared.get("gated"):
                 self.shared_logit = t("shared_logit")
 
     def step_weights(self):
-        return [w for w in (self.router, self.gate_up, self.down, self.bias, self.shared_gate_up, self.shared_down, self.shared_logit)
-                if w is not None]
+        return [w for w in (self.router, self.gate_up, self.down, self.bias, self.correction, self.shared_gate_up, self.shared_down,
+                            self.shared_logit) if w is not None]
 
     def forward(self, x, ctx):
         out = torch.empty_like(x)
@@ -101,7 +128,9 @@ class RoutedExperts(FeedForward):
         extra = None
         if self.shared is not None:   # the expert that every token gets rides on the kernel that sums the chosen ones
             act = torch.empty((x.shape[0], int(self.shared["size"])), dtype=x.dtype, device=x.device)
-            if self.gate == "clamped":
+            if self.gate == "none":
+                ops.bias_act(ops.linear_rows(x, self.shared_gate_up), None, self.activation, act)
+            elif self.gate == "clamped":
                 limit = float(self.shared.get("limit") or self.limit)
                 if not ops.gated_rows(x, self.shared_gate_up, act, clamp=(limit, self.alpha)):   # few rows: the gate in the product
                     ops.clamped_glu(ops.linear_rows(x, self.shared_gate_up), limit, self.alpha, act)
@@ -121,11 +150,31 @@ class RoutedExperts(FeedForward):
         # (the large tile only where both products' operands allow it)
         tile_rows = min(ops.moe_tile_rows(n, self.n_experts, self.top, self.gate_up), ops.moe_tile_rows(n, self.n_experts, self.top, self.down))
         soft, renorm = self.score == "softmax", self.renormalize
+        choice = {"correction": self.correction, "groups": self.groups} if (self.corrected or self.groups) else {}
         if n * self.n_experts <= ops.MOE_FUSED_ROUTER_MAX:
-            plan = ops.moe_plan(None, self.top, soft, renorm, tile_rows, x=x, router=self.router, bias=self.bias)   # few tokens: one launch
+            plan = ops.moe_plan(None, self.top, soft, renorm, tile_rows, x=x, router=self.router, bias=self.bias, **choice)   # few tokens: one launch
         else:
-            plan = ops.moe_plan(ops.linear(x, self.router, out_dtype=torch.float32), self.top, soft, renorm, tile_rows, bias=self.bias)
+            plan = ops.moe_plan(ops.linear(x, self.router, out_dtype=torch.float32), self.top, soft, renorm, tile_rows, bias=self.bias,
+                                **choice)
         self._plan = plan
+        if self.gate == "none":
+            act = torch.empty((plan.pairs, self.inter), dtype=x.dtype, device=x.device)
+            rows = torch.empty((plan.pairs, self.hidden), dtype=x.dtype, device=x.device)
+            if tile_rows == ops.kernels.GROUP_LARGE_TILE_ROWS and ops.tc_gemm_grouped_takes(rows, self.gate_up, plan) \
+                    and ops.tc_gemm_grouped_takes(act, self.down, plan):
+                # long steps: both products on the tcgen05 tensor cores (their tiled copies want the sorted rows in memory)
+                ops.moe_gather(x, plan, rows, False)
+                up = torch.empty_like(act)
+                ops.tc_gemm_grouped(ops.TC_PLAIN, rows, self.gate_up, plan, up, None, ctx.err)
+                ops.bias_act(up, None, self.activation, act)
+                y = torch.empty_like(rows)
+                ops.tc_gemm_grouped(ops.TC_PLAIN, act, self.down, plan, y, None, ctx.err)
+                return RowSum(y, plan.dest, self.top, plan.sorted_weight)
+            up = torch.empty_like(act)
+            ops.expert_linear(x, self.gate_up, plan, up, gather=True)   # the rows are read through the plan's row map
+            ops.bias_act(up, None, self.activation, act)
+            ops.expert_linear(act, self.down, plan, rows)
+            return RowSum(rows, plan.dest, self.top, plan.sorted_weight)
         if self.gate == "clamped":
             act = torch.empty((plan.pairs, self.inter), dtype=x.dtype, device=x.device)
             rows = torch.empty((plan.pairs, self.hidden), dtype=x.dtype, device=x.device)

@@ -9,7 +9,7 @@ from typing import Optional
 import torch
 
 from .. import ops
-from .base import Norm, TensorSpec
+from .base import Norm, PendingScaled, TensorSpec
 from .registry import register_part
 
 
@@ -31,9 +31,14 @@ class RmsNorm(Norm):
     def bind(self, tensors, dtype, device):
         self.weight = tensors[self.file_name("weight")]
 
-    def forward(self, hidden: torch.Tensor, delta: Optional[torch.Tensor]) -> torch.Tensor:
+    def forward(self, hidden: torch.Tensor, delta) -> torch.Tensor:
+        """delta: None, a tensor, or a `PendingScaled` (outputs that enter the stream under a factor each, added by this
+        norm's kernel on its way)."""
         out = torch.empty(hidden.shape, dtype=self.weight.dtype, device=hidden.device)
-        ops.add_rms_norm(hidden, delta, self.weight, self.eps, out)
+        if isinstance(delta, PendingScaled):
+            ops.add_rms_norm_scaled(hidden, delta.a, delta.scale_a, delta.b, delta.scale_b, self.weight, self.eps, out)
+        else:
+            ops.add_rms_norm(hidden, delta, self.weight, self.eps, out)
         return out
 
     def fused_rms(self):

@@ -14,8 +14,21 @@ k, v, q and the two gates come from and in what follows the scan:
       decay = exp(-exp(A_log) dt), take = dt, k = B, q = C (shared by the heads of a group), v = x;
       y <- y + D x;  out = Wo (rms_in_parts(y * silu(z)) * w)
 
+Two more kinds decay every ROW of S by a number of its own (a decay per head and key channel, `ops.outer_state_scan_rows`):
+
+  time_mix (RWKV-style time mixing)
+      with h' the token before (zeros at a sequence's start) each of r, k, v, g, w reads its own mix  h + (h' - h) mu_s;
+      r, k, v = Wr ., Wk ., Wv . in heads of `dim`;  w = exp(-exp(W2 tanh(W1 .) + w0)) per head and channel;
+      y_t = (S + diag(u) k_t v_t^T)^T r_t  with S as it was BEFORE the token (u: a learned bonus for the token itself);
+      S <- diag(w_t) S + k_t v_t^T;   out = Wo (unit_per_head(y) * n * silu(Wg .))
+  gated_linear_attention
+      q = Wq h / sqrt(dim), k = Wk h, v = Wv h in heads;  a = sigmoid(A2 (A1 h) + b)^(1 / tau) per head and key channel;
+      S <- diag(a_t) S + k_t v_t^T;  y_t = S^T q_t (AFTER the token);  out = Wo (rms_per_head(y; n) * silu(Wg h)),
+      the norm's weight [vdim] shared by the heads
+
 The state lives in the sequence cache as ONE float32 row per sequence and schedule entry (`StateNeed`), zeroed when a
-sequence starts: [S | n | m] for the matrix memory, [S | the convolution's last taps - 1 inputs] for the state space.
+sequence starts: [S | n | m] for the matrix memory, [S | the convolution's last taps - 1 inputs] for the state space,
+[S | the last token's h] for the time mixing, [S] for the gated linear attention.
 The gates' pre-activations are products with float32 results, and everything from there to the scan's output is
 float32 in both precisions; the other projections and the convolution carry the activation dtype.
 """
@@ -160,5 +173,145 @@ class StateSpace(Mixer):
         return ops.linear_rows(out, self.o_weight)
 
 
+def _low_rank(params, key="rank") -> int:
+    """The rank of a low-rank pair of matrices: named by the spec, or -1 where only the weight files give it."""
+    return int(params[key]) if params.get(key) else -1
+
+
+class TimeMix(Mixer):
+    """params: hidden_size, num_heads, head_dim, eps, and optionally rank (of the decay's low-rank pair; read from the
+    tensors where absent).
+    tensors: mu_r, mu_k, mu_v, mu_g, mu_w [W]; r_weight, k_weight, v_weight, g_weight [H*dim, W]; w1 [rank, W], w2 [H*dim, rank],
+    w0 [H*dim]; bonus [H, dim]; norm [H*dim]; o_weight [W, H*dim]."""
+
+    MIXES = ("r", "k", "v", "g", "w")
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        p = self.params
+        self.hidden, self.n_heads, self.dim = int(p["hidden_size"]), int(p["num_heads"]), int(p["head_dim"])
+        self.eps, self.rank = float(p["eps"]), _low_rank(p)
+        if self.dim > ops.OUTER_STATE_MAX_DIM:
+            raise ValueError(f"time_mix: head_dim {self.dim} > {ops.OUTER_STATE_MAX_DIM} is not supported by the scan kernel")
+        self.inner = self.n_heads * self.dim
+        self.s_offset, self.h_offset = 0, self.n_heads * self.dim * self.dim
+        self.state_floats = self.h_offset + self.hidden
+        self.mu = self.proj_weight = self.w1 = self.w2 = self.w0 = self.bonus = self.norm = self.o_weight = None
+
+    def tensor_specs(self):
+        f, c, w = self.file_name, self.inner, self.hidden
+        specs = [TensorSpec(f("mu_" + s), (w,), init="fraction", keep="float32") for s in self.MIXES]
+        specs += [TensorSpec(f(s + "_weight"), (c, w)) for s in "rkvg"]
+        return specs + [TensorSpec(f("w1"), (self.rank, w)), TensorSpec(f("w2"), (c, self.rank), init="low_rank"),
+                        TensorSpec(f("w0"), (c,), init="rate", keep="float32"),
+                        TensorSpec(f("bonus"), (self.n_heads, self.dim), init="logit", keep="float32"),
+                        TensorSpec(f("norm"), (c,), init="norm"), TensorSpec(f("o_weight"), (w, c))]
+
+    def kernel_libraries(self, dtype):
+        return {"recurrent", "activation", "grouped_gemm"} | ({"gemm_f32"} if dtype == torch.float32 else {"skinny_gemm"})
+
+    def cache_need(self):
+        return StateNeed((self.state_floats,), torch.float32)
+
+    def bind(self, tensors, dtype, device):
+        t = lambda logical: tensors[self.file_name(logical)]
+        self.mu = torch.stack([t("mu_" + s).to(torch.float32) for s in self.MIXES]).contiguous()       # [5, W]: r, k, v, g, w
+        self.proj_weight = torch.stack([t(s + "_weight") for s in "rkvg"]).contiguous()                  # [4, H*dim, W]
+        self.w1, self.w2 = t("w1").contiguous(), t("w2").contiguous()
+        self.rank = int(self.w1.shape[0])
+        self.w0, self.bonus = t("w0").to(torch.float32).contiguous(), t("bonus").to(torch.float32).contiguous()
+        self.norm, self.o_weight = t("norm"), t("o_weight")
+
+    def step_weights(self):
+        return [self.mu, self.proj_weight, self.w1, self.w2, self.w0, self.bonus, self.norm, self.o_weight]
+
+    def forward(self, x, ctx, site, writes_cache):
+        if not writes_cache:
+            raise ValueError("time_mix: a recurrent state cannot be read from another schedule entry")
+        n, w, h, d, c = x.shape[0], self.hidden, self.n_heads, self.dim, self.inner
+        f32 = dict(dtype=torch.float32, device=x.device)
+        mixes = torch.empty((n, 5 * w), dtype=x.dtype, device=x.device)                 # [T, r | k | v | g | w], each W wide
+        ops.shift_mix(x, self.mu, ctx.cu_q, ctx.tok_seq, ctx.slots, site.storage, self.h_offset, mixes,
+                      single=ctx.is_decode and n == ctx.n_seqs)
+        proj = torch.empty((n, 4 * c), dtype=x.dtype, device=x.device)                  # [T, r | k | v | g]
+        if n > ops.WIDE_MAX_ROWS:   # long steps: a library product per mix
+            for i in range(4):
+                ops.linear(mixes[:, i * w:(i + 1) * w], self.proj_weight[i], out=proj[:, i * c:(i + 1) * c])
+        else:                       # one launch for the four
+            ops.head_linear(mixes[:, :4 * w], self.proj_weight, proj)
+        low = ops.linear_rows(mixes[:, 4 * w:], self.w1)
+        bent = torch.empty_like(low)
+        ops.bias_act(low, None, "tanh", bent)
+        pre = ops.linear_rows(bent, self.w2, out_dtype=torch.float32)                    # float32 sums
+        decay = torch.empty((n, c), **f32)
+        ops.channel_decay(pre, self.w0, "double_exp", decay)
+        y = torch.empty((n, c), **f32)
+        ops.outer_state_scan_rows(proj[:, :c], proj[:, c:2 * c], proj[:, 2 * c:3 * c], decay, ctx.cu_q, ctx.slots, site.storage,
+                                  self.s_offset, h, d, d, 1.0, y, bonus=self.bonus)
+        out = torch.empty((n, c), dtype=x.dtype, device=x.device)
+        ops.gated_group_norm(y, proj[:, 3 * c:], self.norm, self.eps, out, h, h, "silu", False)
+        return ops.linear_rows(out, self.o_weight)
+
+
+class GatedLinearAttention(Mixer):
+    """params: hidden_size, num_heads, head_dim, value_dim, tau, eps, and optionally rank (of the decay's low-rank pair).
+    tensors: q_weight, k_weight [H*dim, W], v_weight, g_weight [H*vdim, W], o_weight [W, H*vdim], norm [vdim],
+    a1 [rank, W], a2 [H*dim, rank], a2_bias [H*dim]."""
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        p = self.params
+        self.hidden, self.n_heads = int(p["hidden_size"]), int(p["num_heads"])
+        self.dim, self.vdim = int(p["head_dim"]), int(p["value_dim"])
+        self.tau, self.eps, self.rank = float(p["tau"]), float(p["eps"]), _low_rank(p)
+        if self.dim > ops.OUTER_STATE_MAX_DIM or self.tau <= 0:
+            raise ValueError(f"gated_linear_attention: head_dim up to {ops.OUTER_STATE_MAX_DIM} and a positive tau are supported")
+        self.state_floats = self.n_heads * self.dim * self.vdim
+        self.proj_weight = self.a1 = self.a2 = self.a2_bias = self.norm = self.o_weight = None
+
+    def tensor_specs(self):
+        f, h, d, v, w = self.file_name, self.n_heads, self.dim, self.vdim, self.hidden
+        return [TensorSpec(f("q_weight"), (h * d, w)), TensorSpec(f("k_weight"), (h * d, w)), TensorSpec(f("v_weight"), (h * v, w)),
+                TensorSpec(f("g_weight"), (h * v, w)), TensorSpec(f("o_weight"), (w, h * v)), TensorSpec(f("norm"), (v,), init="norm"),
+                TensorSpec(f("a1"), (self.rank, w)), TensorSpec(f("a2"), (h * d, self.rank), init="low_rank"),
+                TensorSpec(f("a2_bias"), (h * d,), init="logit", keep="float32")]
+
+    def kernel_libraries(self, dtype):
+        return {"recurrent"} | ({"gemm_f32"} if dtype == torch.float32 else {"skinny_gemm"})
+
+    def cache_need(self):
+        return StateNeed((self.state_floats,), torch.float32)
+
+    def bind(self, tensors, dtype, device):
+        t = lambda logical: tensors[self.file_name(logical)]
+        self.proj_weight = torch.cat((t("q_weight"), t("k_weight"), t("v_weight"), t("g_weight")), dim=0).contiguous()
+        self.a1, self.a2 = t("a1").contiguous(), t("a2").contiguous()
+        self.rank = int(self.a1.shape[0])
+        self.a2_bias = t("a2_bias").to(torch.float32).contiguous()
+        self.norm = t("norm").repeat(self.n_heads).contiguous()      # the one weight [vdim] under every head
+        self.o_weight = t("o_weight")
+
+    def step_weights(self):
+        return [self.proj_weight, self.a1, self.a2, self.a2_bias, self.norm, self.o_weight]
+
+    def forward(self, x, ctx, site, writes_cache):
+        if not writes_cache:
+            raise ValueError("gated_linear_attention: a recurrent state cannot be read from another schedule entry")
+        n, h, d, v = x.shape[0], self.n_heads, self.dim, self.vdim
+        f32 = dict(dtype=torch.float32, device=x.device)
+        proj = ops.linear_rows(x, self.proj_weight)                                      # [T, q | k | v | g]
+        pre = ops.linear_rows(ops.linear_rows(x, self.a1), self.a2, out_dtype=torch.float32)   # float32 sums
+        decay = torch.empty((n, h * d), **f32)
+        ops.channel_decay(pre, self.a2_bias, "sigmoid_root", decay, tau=self.tau)
+        y = torch.empty((n, h * v), **f32)
+        ops.outer_state_scan_rows(proj[:, :h * d], proj[:, h * d:2 * h * d], proj[:, 2 * h * d:2 * h * d + h * v], decay, ctx.cu_q,
+                                  ctx.slots, site.storage, 0, h, d, v, d ** -0.5, y)
+        out = torch.empty((n, h * v), dtype=x.dtype, device=x.device)
+        ops.gated_group_norm(y, proj[:, 2 * h * d + h * v:], self.norm, self.eps, out, h, h, "silu", False)
+        return ops.linear_rows(out, self.o_weight)
+
+
 register_part("mixer", "matrix_memory", MatrixMemory)
+register_part("mixer", "time_mix", TimeMix)
+register_part("mixer", "gated_linear_attention", GatedLinearAttention)
 register_part("mixer", "state_space", StateSpace)

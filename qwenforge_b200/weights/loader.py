@@ -64,6 +64,13 @@ def merge_specs(specs: Iterable[TensorSpec]) -> dict[str, TensorSpec]:
     return merged
 
 
+def shape_matches(stored, wanted) -> bool:
+    """Whether a file's tensor has the wanted shape; a wanted extent of -1 takes any size (a size that only the file gives,
+    such as the rank of a low-rank pair of matrices: the part reads it from the tensor it is bound to)."""
+    stored, wanted = tuple(stored), tuple(wanted)
+    return len(stored) == len(wanted) and all(w == -1 or int(s) == int(w) for s, w in zip(stored, wanted))
+
+
 def kept_dtype(spec: TensorSpec, stored: torch.dtype, compute: torch.dtype) -> torch.dtype:
     if spec.keep == "int32":
         return torch.int32
@@ -110,7 +117,7 @@ def load_weights(model_dir, specs: Iterable[TensorSpec], dtype: torch.dtype, dev
                 continue
             name = source[name]
             stored_dtype, shape = where[name].info(name)
-            if tuple(shape) != tuple(spec.shape):
+            if not shape_matches(shape, spec.shape):
                 wrong_shape.append(f"{name}: file has {list(shape)}, model wants {list(spec.shape)}")
             is_int = not stored_dtype.is_floating_point
             if is_int != (spec.keep == "int32"):

@@ -18,6 +18,9 @@ from .safetensors_io import save_safetensors
 
 
 def draw_tensor(spec: TensorSpec, generator: torch.Generator, store_dtype: torch.dtype) -> torch.Tensor:
+    if any(int(extent) < 0 for extent in spec.shape):
+        raise ValueError(f"tensor {spec.name!r}: an extent that only a weight file gives cannot be drawn at random; "
+                         "name it in the configuration")
     if spec.keep == "int32":
         return torch.zeros(spec.shape, dtype=torch.int32)
     noise = torch.randn(spec.shape, generator=generator, dtype=torch.float32)
@@ -31,6 +34,10 @@ def draw_tensor(spec: TensorSpec, generator: torch.Generator, store_dtype: torch
         value = (1.0 + 0.5 * noise) / spec.shape[-1] ** 0.5
     elif spec.init == "fraction":    # a mixing weight between 0 and 1
         value = torch.sigmoid(noise)
+    elif spec.init == "rate":        # the offset of a decay exp(-exp(.)): decays spread over (0, 1)
+        value = noise - 1.0
+    elif spec.init == "low_rank":    # the second matrix of a low-rank pair that sets a gate: wide enough to move it
+        value = 0.5 * noise
     else:
         raise ValueError(f"tensor {spec.name!r}: unknown init {spec.init!r}")
     return value if spec.keep == "stored" else value.to(store_dtype)
@@ -51,7 +58,7 @@ def random_state_on_device(specs, seed: int, dtype: torch.dtype, device) -> dict
         if spec.keep == "int32":
             out[name] = torch.zeros(spec.shape, dtype=torch.int32, device=device)
             continue
-        if spec.init not in ("norm", "matrix", "bias", "logit", "conv", "fraction"):
+        if spec.init not in ("norm", "matrix", "bias", "logit", "conv", "fraction", "rate", "low_rank"):
             raise ValueError(f"tensor {spec.name!r}: unknown init {spec.init!r}")
         kept = torch.float32 if spec.keep in ("stored", "float32") else dtype
         value = torch.empty(spec.shape, dtype=kept, device=device)
@@ -62,6 +69,10 @@ def random_state_on_device(specs, seed: int, dtype: torch.dtype, device) -> dict
                 noise = (1.0 + 0.5 * noise) / spec.shape[-1] ** 0.5
             elif spec.init == "fraction":
                 noise = torch.sigmoid(noise)
+            elif spec.init == "rate":
+                noise = noise - 1.0
+            elif spec.init == "low_rank":
+                noise = 0.5 * noise
             else:
                 noise = 1.0 + 0.1 * noise if spec.init == "norm" else noise if spec.init == "logit" else 0.02 * noise
             flat[begin:begin + noise.numel()] = noise.to(kept)

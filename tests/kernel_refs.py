@@ -274,14 +274,26 @@ def scaled_swiglu(gate_up, row_scale, out):
     out.copy_((g * torch.sigmoid(g) * u).to(out.dtype))
 
 
-def moe_plan(logits, top, softmax_scores=False, renormalize=False, tile_rows=64, x=None, router=None, bias=None):
+def moe_plan(logits, top, softmax_scores=False, renormalize=False, tile_rows=64, x=None, router=None, bias=None, correction=None,
+             groups=None):
     if logits is None:
         logits = (_f(x) @ _f(router).T)
     z = logits.to(torch.float32)
     if bias is not None:
         z = z + bias.to(torch.float32)
     scores = torch.softmax(z, -1) if softmax_scores else torch.sigmoid(z)
-    chosen = torch.topk(scores, top, dim=-1)
+    if correction is not None or groups is not None:
+        choice = scores if correction is None else scores + correction.to(torch.float32)
+        count, keep = groups if groups is not None else (1, 1)
+        if keep < count:
+            grouped = choice.view(z.shape[0], count, -1)
+            group_score = grouped.topk(min(2, grouped.shape[-1]), dim=-1).values.sum(-1)
+            kept = torch.zeros_like(group_score, dtype=torch.bool).scatter_(1, group_score.topk(keep, dim=-1).indices, True)
+            choice = grouped.masked_fill(~kept[:, :, None], float("-inf")).reshape(z.shape)
+        picked = torch.topk(choice, top, dim=-1).indices
+        chosen = torch.return_types.topk((scores.gather(1, picked), picked))
+    else:
+        chosen = torch.topk(scores, top, dim=-1)
     weights = chosen.values / chosen.values.sum(-1, keepdim=True) if renormalize else chosen.values
     plan = _Routing()
     plan.n_tokens, plan.n_experts, plan.top, plan.pairs = z.shape[0], z.shape[1], top, z.shape[0] * top
@@ -329,9 +341,87 @@ def bias_act(x, bias, kind, out):
         y = z * torch.sigmoid(z)
     elif kind == "gelu":
         y = 0.5 * z * (1 + torch.erf(z / 2 ** 0.5))
+    elif kind == "tanh":
+        y = torch.tanh(z)
     else:
         y = torch.relu(z)
     out.copy_(y.to(out.dtype))
+
+
+def _act(z, kind):
+    out = torch.empty_like(z)
+    bias_act(z, None, kind, out)
+    return out
+
+
+def bias_glu(gate_up, bias, kind, out):
+    inter = out.shape[1]
+    z = _f(gate_up) if bias is None else _f(gate_up) + _f(bias)
+    out.copy_((_act(z[:, :inter], kind) * z[:, inter:]).to(out.dtype))
+
+
+def add_rms_norm_scaled(hidden, a, scale_a, b, scale_b, weight, eps, out):
+    residual_add_scaled(hidden, a, scale_a, b, scale_b)
+    out.copy_(_rms(hidden, weight, eps).to(out.dtype))
+
+
+def residual_add_scaled(hidden, a, scale_a, b=None, scale_b=0.0):
+    t = scale_a * _f(a)
+    if b is not None:
+        t = t + scale_b * _f(b)
+    hidden.add_(t.to(torch.float32))
+
+
+def rms_norm_cols(x, runs, eps):
+    for col0, width, count, weight in runs:
+        v = _f(x[:, col0:col0 + width])
+        x[:, col0:col0 + width] = (v / torch.sqrt(v.square().sum(-1, keepdim=True) / count + eps) * _f(weight)).to(x.dtype)
+
+
+def mix_rows(x, other, heads, size, x_head, other_head, weight):
+    for h in range(heads):
+        mine, theirs = x[:, h * x_head:h * x_head + size], other[:, h * other_head:h * other_head + size]
+        mine.copy_(((1.0 - weight) * _f(mine) + weight * _f(theirs)).to(x.dtype))
+
+
+def shift_mix(h, mu, cu_q, tok_seq, slots, state, offset, out, single=False):
+    width = h.shape[1]
+    for s in range(cu_q.numel() - 1):
+        begin, end, slot = int(cu_q[s]), int(cu_q[s + 1]), int(slots[s])
+        if end <= begin:
+            continue
+        first = _f(state[slot, offset:offset + width]) if slot >= 0 else torch.zeros(width, dtype=torch.float64, device=h.device)
+        mine = _f(h[begin:end])
+        before = torch.cat((first[None], mine[:-1]), dim=0)
+        for i in range(mu.shape[0]):
+            out[begin:end, i * width:(i + 1) * width] = (mine + (before - mine) * _f(mu[i])).to(out.dtype)
+        if slot >= 0:
+            state[slot, offset:offset + width] = mine[-1].float()
+
+
+def channel_decay(pre, bias, kind, out, tau=1.0):
+    z = _f(pre) if bias is None else _f(pre) + _f(bias)
+    w = torch.exp(-torch.exp(z)) if kind == "double_exp" else torch.exp(torch.nn.functional.logsigmoid(z) / tau)
+    out.copy_(w.float())
+
+
+def outer_state_scan_rows(q, k, v, decay, cu_q, slots, state, s_offset, n_heads, dim, vdim, q_scale, y, bonus=None):
+    size = n_heads * dim * vdim
+    for s in range(cu_q.numel() - 1):
+        slot = int(slots[s])
+        S = torch.zeros(n_heads, dim, vdim, dtype=torch.float64, device=q.device)
+        if slot >= 0:
+            S = _f(state[slot, s_offset:s_offset + size]).view(n_heads, dim, vdim).clone()
+        for t in range(int(cu_q[s]), int(cu_q[s + 1])):
+            qt, kt, vt = (_f(q[t]) * q_scale).view(n_heads, dim), _f(k[t]).view(n_heads, dim), _f(v[t]).view(n_heads, vdim)
+            kv = kt[:, :, None] * vt[:, None, :]
+            if bonus is not None:
+                y[t] = torch.einsum("hdv,hd->hv", S + _f(bonus).view(n_heads, dim)[:, :, None] * kv, qt).reshape(-1).float()
+            S = _f(decay[t]).view(n_heads, dim)[:, :, None] * S + kv
+            if bonus is None:
+                y[t] = torch.einsum("hdv,hd->hv", S, qt).reshape(-1).float()
+        if slot >= 0:
+            state[slot, s_offset:s_offset + size] = S.reshape(-1).float()
 
 
 def softcap_(x, cap):
@@ -475,7 +565,9 @@ def pool_cache_write(cu_q, tok_pos, slots, site, blocks, pool, max_q_len, err):
             blocks.storage[page, 1, :, block % PAGE, :] = v.mean(1).to(blocks.storage.dtype)
 
 
-ALL = dict(gated_rows=gated_rows, causal_conv=causal_conv, add_dyt_norm=add_dyt_norm, add_dyt_norm_shift=add_dyt_norm_shift, residual_add_pair=residual_add_pair, stream_pair=stream_pair,
+ALL = dict(bias_glu=bias_glu, add_rms_norm_scaled=add_rms_norm_scaled, residual_add_scaled=residual_add_scaled, rms_norm_cols=rms_norm_cols,
+           mix_rows=mix_rows, shift_mix=shift_mix, channel_decay=channel_decay, outer_state_scan_rows=outer_state_scan_rows,
+           gated_rows=gated_rows, causal_conv=causal_conv, add_dyt_norm=add_dyt_norm, add_dyt_norm_shift=add_dyt_norm_shift, residual_add_pair=residual_add_pair, stream_pair=stream_pair,
            head_gate=head_gate, pool_cache_write=pool_cache_write, bias_act=bias_act, softcap_=softcap_, stabilized_gates=stabilized_gates, decay_gates=decay_gates,
            outer_state_scan=outer_state_scan, gated_group_norm=gated_group_norm, causal_conv_silu=causal_conv_silu,
            expert_gate_takes=expert_gate_takes, linear_rows=linear_rows, moe_tile_rows=moe_tile_rows, scaled_swiglu=scaled_swiglu, embed_positions=embed_positions, sandwich_norm=sandwich_norm, clamped_glu=clamped_glu, latent_norm_cache=latent_norm_cache,
