@@ -6,6 +6,7 @@ decode at batch 1 and 64, and the same decode rate end to end through the Python
     python bench.py --design mefepel     # instead: the Mefepel presets beside the Qwen2 presets of equal layer sizes
     python bench.py --design zebovik     # the same for the Zebovik presets (attention in blocks, mLSTM and Mamba-2 layers)
     python bench.py --design rarevik     # the same for the Rarevik presets (parallel layers, windows with pooled blocks, routed experts)
+    python bench.py --design gatosun     # the same for the Gatosun presets (window attention beside time mixing, gated linear attention, experts in groups)
                                          # (prompt and decode rates, device times by kind of kernel), as one JSON line
 
 One decode step = one token for every sequence of the batch. The K timed steps are the last K steps before
@@ -45,7 +46,7 @@ def parse():
     p.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
                    help="run only this named workload (3B: 16 unequal prompts then 256 steps; 7B: batch 64 to context "
                         "8192 at temperature 0.7) and print its line")
-    p.add_argument("--design", default=None, choices=["mefepel", "zebovik", "rarevik"],
+    p.add_argument("--design", default=None, choices=["mefepel", "zebovik", "rarevik", "gatosun"],
                    help="measure another design's prefill and decode beside the Qwen2 model of equal size (kernel by "
                         "kernel), instead of the default workload")
     p.add_argument("--no-workloads", action="store_true", help="leave the 3B and 7B workloads out of the default run's points")
@@ -359,7 +360,8 @@ class _StubTokenizer:
 # Another design beside the Qwen2 model of the same layer sizes: (its preset, the Qwen2 preset, layers to run of both).
 DESIGN_PAIRS = {"mefepel": [("mefepel-0.5b", "qwen2.5-0.5b", None), ("mefepel-3b", "qwen2.5-3b", None)],
                 "zebovik": [("zebovik-0.5b", "qwen2.5-0.5b", None), ("zebovik-3b", "qwen2.5-3b", None)],
-                "rarevik": [("rarevik-0.5b", "qwen2.5-0.5b", None), ("rarevik-3b", "qwen2.5-3b", None)]}
+                "rarevik": [("rarevik-0.5b", "qwen2.5-0.5b", None), ("rarevik-3b", "qwen2.5-3b", None)],
+                "gatosun": [("gatosun-0.5b", "qwen2.5-0.5b", None), ("gatosun-3b", "qwen2.5-3b", None)]}
 # what a kernel's label (ops/timing.py) counts as, so that like is laid beside like
 KERNEL_KINDS = (("attention_prefill", "attention (prompt)"), ("attention_decode", "attention (decode)"),
                 ("attention_generic", "attention (plain)"), ("head_linear", "per-head products"),
@@ -369,6 +371,8 @@ KERNEL_KINDS = (("attention_prefill", "attention (prompt)"), ("attention_decode"
                 ("fold_project", "fold + output projection"), ("norm", "norms"), ("residual_add", "norms"),
                 ("rope_cache_write", "rotation + cache write"), ("latent_norm_cache", "latent norms + cache write"),
                 ("swiglu", "gates"), ("clamped_glu", "gates"), ("bias_act", "gates"), ("softcap_", "capped logits"),
+                ("add_rms_norm_scaled", "norms"), ("rms_norm_cols", "norms of q and k over whole rows"), ("mix_rows", "values drawn towards an earlier layer's"),
+                ("bias_glu", "gates"), ("shift_mix", "token shift"), ("channel_decay", "recurrent gates"),
                 ("outer_state_scan", "recurrent scan"), ("stabilized_gates", "recurrent gates"), ("decay_gates", "recurrent gates"),
                 ("gated_group_norm", "gated norm after the scan"), ("causal_conv_silu", "convolution"), ("causal_conv", "convolution"),
                 ("add_dyt_norm", "norms"), ("stream_pair", "norms"), ("head_gate", "gates"), ("pool_cache_write", "pooled rows of blocks"), ("embed", "embedding"), ("gather_rows", "gather + final norm"))

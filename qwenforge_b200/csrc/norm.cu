@@ -466,8 +466,8 @@ QF_EXPORT int qf_stream_pair(int is_bf16, const float* hidden, const void* a, co
 //   t = sa * a;  t = fma(sb, b, t);  hidden = hidden + t.
 template <typename T>
 __device__ __forceinline__ float scaled_terms(const T* a, float sa, const T* b, float sb, size_t i) {
-    float t = sa * Num<T>::to_f(a[i]);
-    if (b) t = fmaf(sb, Num<T>::to_f(b[i]), t);
+    float t = __fmul_rn(sa, Num<T>::to_f(a[i]));   // (intrinsics: the compiler must not fuse these with the addition after them)
+    if (b) t = __fmaf_rn(sb, Num<T>::to_f(b[i]), t);
     return t;
 }
 
@@ -480,7 +480,7 @@ add_scaled_rms_norm_kernel(float* __restrict__ hidden, const T* __restrict__ a, 
     const size_t row0 = (size_t)blockIdx.x * width;
     float ss = 0.f;
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        const float v = hidden[row0 + c] + scaled_terms(a, sa, b, sb, row0 + c);
+        const float v = __fadd_rn(hidden[row0 + c], scaled_terms(a, sa, b, sb, row0 + c));
         hidden[row0 + c] = v;
         ss += v * v;
     }
@@ -513,12 +513,12 @@ add_scaled_rms_norm_warp_kernel(float* __restrict__ hidden, const T* __restrict_
     for (int u = 0; u < NW_MAX; ++u) {
         const int c = lane + 32 * u;
         if (c < n4) {
-            float4 t = make_float4(sa * av[u].x, sa * av[u].y, sa * av[u].z, sa * av[u].w);
-            if (b) t = make_float4(fmaf(sb, bv[u].x, t.x), fmaf(sb, bv[u].y, t.y), fmaf(sb, bv[u].z, t.z), fmaf(sb, bv[u].w, t.w));
-            v[u].x += t.x;
-            v[u].y += t.y;
-            v[u].z += t.z;
-            v[u].w += t.w;
+            float4 t = make_float4(__fmul_rn(sa, av[u].x), __fmul_rn(sa, av[u].y), __fmul_rn(sa, av[u].z), __fmul_rn(sa, av[u].w));
+            if (b) t = make_float4(__fmaf_rn(sb, bv[u].x, t.x), __fmaf_rn(sb, bv[u].y, t.y), __fmaf_rn(sb, bv[u].z, t.z), __fmaf_rn(sb, bv[u].w, t.w));
+            v[u].x = __fadd_rn(v[u].x, t.x);
+            v[u].y = __fadd_rn(v[u].y, t.y);
+            v[u].z = __fadd_rn(v[u].z, t.z);
+            v[u].w = __fadd_rn(v[u].w, t.w);
             Vec4<float>::store(hidden + row0 + 4 * c, v[u]);
         }
         ss += v[u].x * v[u].x + v[u].y * v[u].y + v[u].z * v[u].z + v[u].w * v[u].w;
@@ -560,7 +560,7 @@ residual_add_scaled_kernel(float* __restrict__ hidden, const T* __restrict__ a, 
                            size_t total) {
     grid_chain_entry();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
-        hidden[i] += scaled_terms(a, sa, b, sb, i);
+        hidden[i] = __fadd_rn(hidden[i], scaled_terms(a, sa, b, sb, i));
 }
 
 QF_EXPORT int qf_residual_add_scaled(int is_bf16, float* hidden, const void* a, float sa, const void* b, float sb, long long n,

@@ -20,7 +20,8 @@ TIMED = ("embed_gather", "gather_rows", "add_rms_norm", "residual_add", "linear"
          "sandwich_norm", "clamped_glu", "latent_norm_cache", "head_linear", "expert_linear", "moe_plan", "moe_gather",
          "moe_combine", "tc_gemm_grouped", "scaled_swiglu", "linear_rows", "bias_act", "softcap_", "outer_state_scan", "stabilized_gates",
          "decay_gates", "gated_group_norm", "causal_conv_silu", "causal_conv", "add_dyt_norm", "add_dyt_norm_shift", "residual_add_pair", "stream_pair",
-         "head_gate", "pool_cache_write")
+         "head_gate", "pool_cache_write", "add_rms_norm_scaled", "residual_add_scaled", "rms_norm_cols", "mix_rows", "bias_glu",
+         "shift_mix", "channel_decay", "outer_state_scan_rows")
 
 
 class KernelTimer:
