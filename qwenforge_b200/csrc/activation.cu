@@ -134,17 +134,6 @@ QF_EXPORT int qf_scaled_swiglu(int is_bf16, const void* gu, const float* row_sca
 
 // out = act(x + bias): the first half of a feed-forward without a gate. kind 0: the square of relu, 1: tanh-GELU,
 // 2: silu, 3: relu, 4: GELU in its exact form, z Phi(z) through erf, 5: tanh. Float32 inside; bias may be null.
-__device__ __forceinline__ float activate(float z, int kind) {
-    if (kind == 0) {
-        const float r = fmaxf(z, 0.f);
-        return r * r;
-    }
-    if (kind == 1) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
-    if (kind == 2) return z / (1.f + expf(-z));
-    if (kind == 4) return 0.5f * z * (1.f + erff(z * 0.7071067811865476f));
-    if (kind == 5) return tanhf(z);
-    return fmaxf(z, 0.f);
-}
 
 template <typename T>
 __global__ void bias_act_kernel(const T* __restrict__ x, const T* __restrict__ bias, T* __restrict__ out, int width, size_t total,

@@ -68,6 +68,20 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     return scratch[32];
 }
 
+// The activations that kernels apply by number. 0: the square of relu, 1: tanh-GELU, 2: silu, 3: relu, 4: GELU in its exact
+// form (z Phi(z) through erf), 5: tanh. Float32.
+__device__ __forceinline__ float activate(float z, int kind) {
+    if (kind == 0) {
+        const float r = fmaxf(z, 0.f);
+        return r * r;
+    }
+    if (kind == 1) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    if (kind == 2) return z / (1.f + expf(-z));
+    if (kind == 4) return 0.5f * z * (1.f + erff(z * 0.7071067811865476f));
+    if (kind == 5) return tanhf(z);
+    return fmaxf(z, 0.f);
+}
+
 // Where one sequence's keys and values of one schedule entry lie.
 //   base        first element of this entry's storage: [pages][2 (k,v)][kv_heads][QF_PAGE][head_dim]
 //   page_elems  elements per page = 2 * kv_heads * QF_PAGE * head_dim

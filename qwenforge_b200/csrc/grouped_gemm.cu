@@ -34,6 +34,7 @@ struct GroupedArgs {
     const int* a_rows;       // null: row r of A is row r
     const float* row_scale;  // gated tiles: a factor per row on both halves before the gate (null: 1)
     float gate_limit, gate_alpha;   // gated tiles, gate_limit > 0: the clamped gate min(g, limit) sigmoid(alpha g) (clamp(u) + 1)
+    int act;                 // products without a gate: 0 stores the sums; k + 1 stores activate(sum, k) (see common.cuh)
 };
 
 // Which group and which rows this block has; false if it has none.
@@ -105,7 +106,7 @@ grouped_gemm_plain_kernel(GroupedArgs g) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int gn = n0 + tx + 16 * j;
-            if (gn < N) C[(long long)gm * g.ldc + gn] = Num<T>::from_f(acc[i][j]);
+            if (gn < N) C[(long long)gm * g.ldc + gn] = Num<T>::from_f(g.act ? activate(acc[i][j], g.act - 1) : acc[i][j]);
         }
     }
 }
@@ -234,7 +235,11 @@ grouped_gemm_mma_kernel(GroupedArgs g) {
             for (int j = 0; j < 4; ++j) {
                 const int gn = n0 + 32 * wx + 8 * j + 2 * (lane & 3);
                 bf16* dst = C + (long long)gm * g.ldc + gn;
-                const float v0 = acc[i][j][2 * half], v1 = acc[i][j][2 * half + 1];
+                float v0 = acc[i][j][2 * half], v1 = acc[i][j][2 * half + 1];
+                if (g.act) {
+                    v0 = activate(v0, g.act - 1);
+                    v1 = activate(v1, g.act - 1);
+                }
                 if (gn + 1 < N && (((uintptr_t)dst) & 3) == 0) *reinterpret_cast<uint32_t*>(dst) = pack_bf16(v0, v1);
                 else {
                     if (gn < N) dst[0] = __float2bfloat16_rn(v0);
@@ -324,7 +329,11 @@ grouped_gemm_mma_large_kernel(GroupedArgs g) {
             for (int j = 0; j < 4; ++j) {
                 const int gn = n0 + 32 * wx + 8 * j + 2 * (lane & 3);
                 bf16* dst = C + (long long)gm * g.ldc + gn;
-                const float v0 = acc[i][j][2 * half], v1 = acc[i][j][2 * half + 1];
+                float v0 = acc[i][j][2 * half], v1 = acc[i][j][2 * half + 1];
+                if (g.act) {
+                    v0 = activate(v0, g.act - 1);
+                    v1 = activate(v1, g.act - 1);
+                }
                 if (gn + 1 < N && (((uintptr_t)dst) & 3) == 0) *reinterpret_cast<uint32_t*>(dst) = pack_bf16(v0, v1);
                 else {
                     if (gn < N) dst[0] = __float2bfloat16_rn(v0);
@@ -346,14 +355,17 @@ static bool mma_takes(const GroupedArgs& g) {
 // c_group_cols are then not used), whose tiles have `tile_rows` rows: 64, or 128 for the large tile (bfloat16 with aligned
 // operands only: see qf_grouped_gemm_large_takes). A, W and C share the activation dtype; a_rows: see the top.
 // gate_limit > 0 (gated products only): the clamped form of the gate with this limit and the slope gate_alpha.
-QF_EXPORT int qf_grouped_gemm_gate(int is_bf16, const void* a, long long lda, long long a_group_cols, const void* w,
-                                   long long w_group_stride, long long ldw, void* c, long long ldc, long long c_group_cols,
-                                   int rows, int n, int k, int n_groups, const int* tile_group, const int* tile_row0,
-                                   const int* offsets, const int* n_tiles, int max_tiles, int tile_rows, const int* a_rows,
-                                   int gated, const float* row_scale, float gate_limit, float gate_alpha, cudaStream_t stream) {
+// act (products without a gate): 0 stores the sums, k + 1 stores activation k of them (the numbers of common.cuh).
+QF_EXPORT int qf_grouped_gemm_act(int is_bf16, const void* a, long long lda, long long a_group_cols, const void* w,
+                                  long long w_group_stride, long long ldw, void* c, long long ldc, long long c_group_cols,
+                                  int rows, int n, int k, int n_groups, const int* tile_group, const int* tile_row0,
+                                  const int* offsets, const int* n_tiles, int max_tiles, int tile_rows, const int* a_rows,
+                                  int gated, const float* row_scale, float gate_limit, float gate_alpha, int act,
+                                  cudaStream_t stream) {
     if (rows <= 0 || n <= 0 || n_groups <= 0) return 0;
+    if (act < 0 || act > 6 || (gated && act)) return (int)cudaErrorInvalidValue;
     GroupedArgs g{a, lda, a_group_cols, w, w_group_stride, ldw, c, ldc, c_group_cols, rows, n, k, n_groups,
-                  tile_group, tile_row0, offsets, n_tiles, max_tiles, a_rows, row_scale, gate_limit, gate_alpha};
+                  tile_group, tile_row0, offsets, n_tiles, max_tiles, a_rows, row_scale, gate_limit, gate_alpha, act};
     if (gated) {  // n = columns of the result (half of a group's weight rows); the small tensor-core tile only
         if (!is_bf16 || !mma_takes(g) || (tile_group && tile_rows != QF_GROUP_BM)) return (int)cudaErrorInvalidValue;
         const dim3 grid((n + GG_BN / 2 - 1) / (GG_BN / 2), tile_group ? max_tiles : (rows + QF_GROUP_BM - 1) / QF_GROUP_BM, tile_group ? 1 : n_groups);
@@ -378,6 +390,16 @@ QF_EXPORT int qf_grouped_gemm_gate(int is_bf16, const void* a, long long lda, lo
     return (int)launch_pdl(grouped_gemm_plain_kernel<float>, grid, dim3(256), 0, stream, g);
 }
 
+QF_EXPORT int qf_grouped_gemm_gate(int is_bf16, const void* a, long long lda, long long a_group_cols, const void* w,
+                                   long long w_group_stride, long long ldw, void* c, long long ldc, long long c_group_cols,
+                                   int rows, int n, int k, int n_groups, const int* tile_group, const int* tile_row0,
+                                   const int* offsets, const int* n_tiles, int max_tiles, int tile_rows, const int* a_rows,
+                                   int gated, const float* row_scale, float gate_limit, float gate_alpha, cudaStream_t stream) {
+    return qf_grouped_gemm_act(is_bf16, a, lda, a_group_cols, w, w_group_stride, ldw, c, ldc, c_group_cols, rows, n, k, n_groups,
+                               tile_group, tile_row0, offsets, n_tiles, max_tiles, tile_rows, a_rows, gated, row_scale, gate_limit,
+                               gate_alpha, 0, stream);
+}
+
 QF_EXPORT int qf_grouped_gemm(int is_bf16, const void* a, long long lda, long long a_group_cols, const void* w,
                               long long w_group_stride, long long ldw, void* c, long long ldc, long long c_group_cols,
                               int rows, int n, int k, int n_groups, const int* tile_group, const int* tile_row0,
@@ -391,6 +413,6 @@ QF_EXPORT int qf_grouped_gemm(int is_bf16, const void* a, long long lda, long lo
 // Whether a ragged product of these operands may use tiles of 128 rows (the plan has to be cut accordingly).
 QF_EXPORT int qf_grouped_gemm_large_takes(int is_bf16, const void* a, long long lda, const void* w, long long w_group_stride,
                                           long long ldw, int k) {
-    GroupedArgs g{a, lda, 0, w, w_group_stride, ldw, nullptr, 0, 0, 0, 0, k, 0, nullptr, nullptr, nullptr, nullptr, 0, nullptr, nullptr};
+    GroupedArgs g{a, lda, 0, w, w_group_stride, ldw, nullptr, 0, 0, 0, 0, k, 0, nullptr, nullptr, nullptr, nullptr, 0, nullptr, nullptr, 0.f, 0.f, 0};
     return is_bf16 && mma_takes(g) ? 1 : 0;
 }

@@ -638,3 +638,69 @@ QF_EXPORT int qf_mix_rows(int is_bf16, void* x, int ldx, const void* other, int 
     return (int)launch_pdl(mix_rows_kernel<float>, dim3(elementwise_blocks(total)), dim3(256), 0, stream, (float*)x, ldx,
                            (const float*)other, ldo, heads, size, x_head, other_head, lambda, total);
 }
+
+// ------------------------------------------------------------------------------------------------------------------
+// What stands between a q | k | v product and the rotation in a layer that norms q and k over their whole rows, as one
+// kernel, in place: for each of up to three runs of columns (q, k, v) of x[t]
+//   v <- x + bias                                      (bias may be null; rounded to the activation type, as a product's
+//                                                       epilogue would leave it)
+//   the mixing run only:  v[h * x_head + c] <- (1 - lambda) v + lambda other[t][h * other_head + c],  c < size
+//   count > 0:  v <- v / sqrt(sum(v^2) / count + eps) * weight      (count 0: no norm)
+// A block per (row, run). Statistics, mixing and scaling are float32.
+struct PrepRun {
+    int col0, width, count;
+    const void* bias;
+    const void* weight;
+};
+struct PrepMix {
+    int run;   // which run mixes (-1: none)
+    const void* other;
+    int ldo, size, x_head, other_head;
+    float lambda;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+rows_prepare_kernel(T* __restrict__ x, int ld, PrepRun r0, PrepRun r1, PrepRun r2, PrepMix mix, float eps) {
+    grid_chain_entry();
+    __shared__ float scratch[33];
+    const PrepRun r = blockIdx.y == 0 ? r0 : (blockIdx.y == 1 ? r1 : r2);
+    T* row = x + (size_t)blockIdx.x * ld + r.col0;
+    const T* bias = (const T*)r.bias;
+    const bool mixes = mix.run == (int)blockIdx.y;
+    const T* other = mixes ? (const T*)mix.other + (size_t)blockIdx.x * mix.ldo : nullptr;
+    const float keep = 1.0f - mix.lambda;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < r.width; c += blockDim.x) {
+        float v = Num<T>::to_f(row[c]);
+        if (bias) v = Num<T>::to_f(Num<T>::from_f(v + Num<T>::to_f(bias[c])));
+        if (mixes) {
+            const int h = c / mix.x_head, cc = c % mix.x_head;
+            if (cc < mix.size) v = Num<T>::to_f(Num<T>::from_f(fmaf(mix.lambda, Num<T>::to_f(other[(size_t)h * mix.other_head + cc]), keep * v)));
+        }
+        if (bias || mixes) row[c] = Num<T>::from_f(v);
+        ss += v * v;
+    }
+    if (r.count <= 0) return;
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)r.count + eps);
+    const T* w = (const T*)r.weight;
+    // each thread reads back the columns it wrote itself
+    for (int c = threadIdx.x; c < r.width; c += blockDim.x) row[c] = Num<T>::from_f(Num<T>::to_f(row[c]) * inv * Num<T>::to_f(w[c]));
+}
+
+// runs: n_runs (1..3) records of (col0, width, count, bias, weight) as parallel arrays; mix_run -1 for none.
+QF_EXPORT int qf_rows_prepare(int is_bf16, void* x, int ld, int rows, int n_runs, const int* col0, const int* width, const int* count,
+                              const void* const* bias, const void* const* weight, int mix_run, const void* other, int ldo,
+                              int mix_size, int x_head, int other_head, float lambda, float eps, cudaStream_t stream) {
+    if (rows <= 0 || n_runs <= 0) return 0;
+    if (n_runs > 3 || mix_run >= n_runs) return (int)cudaErrorInvalidValue;
+    PrepRun r[3] = {};
+    for (int i = 0; i < n_runs; ++i) {
+        r[i] = PrepRun{col0[i], width[i], count[i], bias[i], weight[i]};
+        if (count[i] > 0 && !weight[i]) return (int)cudaErrorInvalidValue;
+    }
+    const PrepMix mix = {mix_run, other, ldo, mix_size, x_head > 0 ? x_head : 1, other_head, lambda};
+    if (is_bf16)
+        return (int)launch_pdl(rows_prepare_kernel<bf16>, dim3(rows, n_runs), dim3(128), 0, stream, (bf16*)x, ld, r[0], r[1], r[2], mix, eps);
+    return (int)launch_pdl(rows_prepare_kernel<float>, dim3(rows, n_runs), dim3(128), 0, stream, (float*)x, ld, r[0], r[1], r[2], mix, eps);
+}

@@ -146,7 +146,8 @@ outer_state_scan_kernel(const T* __restrict__ q, int q_stride, const T* __restri
                         int v_stride, const float* __restrict__ decay, const float* __restrict__ take,
                         const int* __restrict__ cu_q, const int* __restrict__ slots, float* __restrict__ state,
                         long long slot_stride, long long s_offset, long long n_offset, int n_heads, int n_groups, int dim,
-                        int vdim, float q_scale, float* __restrict__ y, float* __restrict__ nq, const float* __restrict__ bonus) {
+                        int vdim, float q_scale, float* __restrict__ y, float* __restrict__ nq, const float* __restrict__ bonus,
+                        const float* __restrict__ decay_bias, int decay_kind, float inv_tau) {
     grid_chain_entry();
     extern __shared__ __align__(16) float scan_smem[];
     constexpr int THREADS = 32 * WARPS, PARTS = 2 * WARPS, padded = PARTS * ROWS;   // padded >= dim
@@ -182,7 +183,14 @@ outer_state_scan_kernel(const T* __restrict__ q, int q_stride, const T* __restri
     constexpr int QK_EACH = SCAN_TOKENS * padded / THREADS;
     constexpr int V_EACH = (SCAN_TOKENS * SCAN_COLS + THREADS - 1) / THREADS;
     float q_next[QK_EACH], k_next[QK_EACH], v_next[V_EACH], gate_next[2] = {0.f, 0.f};
-    float w_next[MODE != 0 ? QK_EACH : 1], u_row[MODE == 2 ? ROWS : 1];
+    float w_next[MODE != 0 ? QK_EACH : 1], u_row[MODE == 2 ? ROWS : 1], bias_row[MODE != 0 ? QK_EACH : 1];
+    if constexpr (MODE != 0) {   // the bias of the decays this thread will turn: its elements sit at fixed rows of S
+#pragma unroll
+        for (int u = 0; u < QK_EACH; ++u) {
+            const int d = (threadIdx.x + u * THREADS) % padded;
+            bias_row[u] = (decay_kind != 0 && d < dim) ? decay_bias[(size_t)head * dim + d] : 0.f;
+        }
+    }
     if constexpr (MODE == 2) {
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) u_row[r] = d0 + r < dim ? bonus[(size_t)head * dim + d0 + r] : 0.f;
@@ -215,7 +223,17 @@ outer_state_scan_kernel(const T* __restrict__ q, int q_stride, const T* __restri
         for (int u = 0; u < QK_EACH; ++u) {
             q_s[threadIdx.x + u * THREADS] = q_next[u];
             k_s[threadIdx.x + u * THREADS] = k_next[u];
-            if constexpr (MODE != 0) w_s[threadIdx.x + u * THREADS] = w_next[u];
+            if constexpr (MODE != 0) {
+                // the decay itself, or its pre-activation, turned into the decay here, where the load has long arrived (in `fetch`
+                // the arithmetic would wait for it): exp(-exp(z + b)) (kind 1), sigmoid(z + b)^(1 / tau) (kind 2); padding stays 0
+                float w = w_next[u];
+                const int d = (threadIdx.x + u * THREADS) % padded;
+                if (decay_kind != 0 && d < dim) {
+                    const float z = w + bias_row[u];
+                    w = decay_kind == 1 ? expf(-expf(z)) : expf(log_sigmoid(z) * inv_tau);
+                }
+                w_s[threadIdx.x + u * THREADS] = w;
+            }
         }
 #pragma unroll
         for (int u = 0; u < V_EACH; ++u) {
@@ -235,7 +253,7 @@ outer_state_scan_kernel(const T* __restrict__ q, int q_stride, const T* __restri
         stash();
         __syncthreads();
         if (t0 + SCAN_TOKENS < end) fetch(t0 + SCAN_TOKENS);   // on its way while this tile is worked on
-        auto token = [&](int j) {
+        auto token_rows = [&](int j) -> float {   // MODE 1 and 2: one token's update of this half warp's rows, and their part of y
             if constexpr (MODE != 0) {
                 const float add = v_s[j * SCAN_COLS + c16];
                 const float* kj = k_s + j * padded + d0;
@@ -265,9 +283,11 @@ outer_state_scan_kernel(const T* __restrict__ q, int q_stride, const T* __restri
                         }
                     }
                 }
-                part_s[(part * SCAN_TOKENS + j) * SCAN_COLS + c16] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-                return;
+                return (acc[0] + acc[1]) + (acc[2] + acc[3]);
             }
+            return 0.f;
+        };
+        auto token = [&](int j) {
             const float keep = decay_s[j], add = take_s[j] * v_s[j * SCAN_COLS + c16];
             const float* kj = k_s + j * padded + d0;
             const float* qj = q_s + j * padded + d0;
@@ -291,7 +311,19 @@ outer_state_scan_kernel(const T* __restrict__ q, int q_stride, const T* __restri
             }
             part_s[(part * SCAN_TOKENS + j) * SCAN_COLS + c16] = (a0 + a1) + (a2 + a3);
         };
-        if (n_here == SCAN_TOKENS) {   // a whole tile: the tokens' code laid out one after another, addresses as constants
+        if constexpr (MODE != 0) {
+            if (n_here == SCAN_TOKENS) {
+                // a whole tile: the tokens' parts of y stay in registers until the tile is done, so that no store stands between
+                // one token's loads from shared memory and the next one's and the loads run ahead of the chain of updates
+                float parts[SCAN_TOKENS];
+#pragma unroll
+                for (int j = 0; j < SCAN_TOKENS; ++j) parts[j] = token_rows(j);
+#pragma unroll
+                for (int j = 0; j < SCAN_TOKENS; ++j) part_s[(part * SCAN_TOKENS + j) * SCAN_COLS + c16] = parts[j];
+            } else {
+                for (int j = 0; j < n_here; ++j) part_s[(part * SCAN_TOKENS + j) * SCAN_COLS + c16] = token_rows(j);
+            }
+        } else if (n_here == SCAN_TOKENS) {   // a whole tile: the tokens' code laid out one after another, addresses as constants
 #pragma unroll
             for (int j = 0; j < SCAN_TOKENS; ++j) token(j);
         } else {
@@ -319,7 +351,8 @@ template <typename T, int WARPS, int ROWS, int MODE>
 static int launch_scan(const void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride, const float* decay,
                        const float* take, const int* cu_q, const int* slots, int n_seqs, float* state, long long slot_stride,
                        long long s_offset, long long n_offset, int n_heads, int n_groups, int dim, int vdim, float q_scale,
-                       float* y, float* nq, const float* bonus, cudaStream_t stream) {
+                       float* y, float* nq, const float* bonus, const float* decay_bias, int decay_kind, float inv_tau,
+                       cudaStream_t stream) {
     const int columns = vdim + (n_offset >= 0 ? 1 : 0);
     constexpr int PARTS = 2 * WARPS, padded = PARTS * ROWS;
     const size_t smem = (size_t)((MODE != 0 ? 3 : 2) * SCAN_TOKENS * padded + SCAN_TOKENS * SCAN_COLS + PARTS * SCAN_TOKENS * SCAN_COLS + 2 * SCAN_TOKENS) * sizeof(float);
@@ -327,11 +360,12 @@ static int launch_scan(const void* q, int q_stride, const void* k, int k_stride,
     if (e != cudaSuccess) return (int)e;
     return (int)launch_pdl(outer_state_scan_kernel<T, WARPS, ROWS, MODE>, dim3((columns + SCAN_COLS - 1) / SCAN_COLS, n_heads, n_seqs),
                            dim3(32 * WARPS), smem, stream, (const T*)q, q_stride, (const T*)k, k_stride, (const T*)v, v_stride, decay,
-                           take, cu_q, slots, state, slot_stride, s_offset, n_offset, n_heads, n_groups, dim, vdim, q_scale, y, nq, bonus);
+                           take, cu_q, slots, state, slot_stride, s_offset, n_offset, n_heads, n_groups, dim, vdim, q_scale, y, nq, bonus, decay_bias,
+                           decay_kind, inv_tau);
 }
 
 #define QF_SCAN_ARGS q, q_stride, k, k_stride, v, v_stride, decay, take, cu_q, slots, n_seqs, state, slot_stride, s_offset, \
-                     n_offset, n_heads, n_groups, dim, vdim, q_scale, y, nq, bonus, stream
+                     n_offset, n_heads, n_groups, dim, vdim, q_scale, y, nq, bonus, decay_bias, decay_kind, inv_tau, stream
 // 2 * WARPS half warps of ROWS rows each cover `dim` rows
 #define QF_SCAN_CASE(WARPS, ROWS) \
     if (dim <= 2 * WARPS * ROWS)  \
@@ -348,6 +382,9 @@ QF_EXPORT int qf_outer_state_scan(int is_bf16, const void* q, int q_stride, cons
     if (dim <= 0 || vdim <= 0 || n_groups <= 0 || n_heads % n_groups || (n_offset >= 0 && !nq)) return (int)cudaErrorInvalidValue;
     constexpr int MODE = 0;
     const float* bonus = nullptr;
+    const float* decay_bias = nullptr;
+    const int decay_kind = 0;
+    const float inv_tau = 1.f;
     QF_SCAN_CASE(4, 4)
     QF_SCAN_CASE(8, 4)
     QF_SCAN_CASE(16, 4)
@@ -359,7 +396,7 @@ template <int MODE>
 static int scan_rows(int is_bf16, const void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride,
                      const float* decay, const int* cu_q, const int* slots, int n_seqs, float* state, long long slot_stride,
                      long long s_offset, int n_heads, int n_groups, int dim, int vdim, float q_scale, float* y, const float* bonus,
-                     cudaStream_t stream) {
+                     const float* decay_bias, int decay_kind, float inv_tau, cudaStream_t stream) {
     const float* take = nullptr;
     float* nq = nullptr;
     const long long n_offset = -1;
@@ -372,17 +409,22 @@ static int scan_rows(int is_bf16, const void* q, int q_stride, const void* k, in
 
 // The scan with a decay per row of S: decay is float32 [T][heads * dim]; `bonus` null: the output is read after the token's
 // update (MODE 1); `bonus` float32 [heads][dim]: before it, the token's own outer product entering under the bonus (MODE 2).
+// decay_kind 0: `decay` holds the decays; 1 and 2: it holds their pre-activations z and the kernel forms exp(-exp(z + b)) or
+// sigmoid(z + b)^(1 / tau) on its way in (b = decay_bias, float32 [heads * dim]; the arithmetic of `channel_decay_kernel`).
 QF_EXPORT int qf_outer_state_scan_rows(int is_bf16, const void* q, int q_stride, const void* k, int k_stride, const void* v,
                                        int v_stride, const float* decay, const int* cu_q, const int* slots, int n_seqs,
                                        float* state, long long slot_stride, long long s_offset, int n_heads, int n_groups, int dim,
-                                       int vdim, float q_scale, float* y, const float* bonus, cudaStream_t stream) {
+                                       int vdim, float q_scale, float* y, const float* bonus, const float* decay_bias,
+                                       int decay_kind, float inv_tau, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
-    if (dim <= 0 || vdim <= 0 || n_groups <= 0 || n_heads % n_groups || !decay) return (int)cudaErrorInvalidValue;
+    if (dim <= 0 || vdim <= 0 || n_groups <= 0 || n_heads % n_groups || !decay || decay_kind < 0 || decay_kind > 2 ||
+        (decay_kind != 0 && !decay_bias))
+        return (int)cudaErrorInvalidValue;
     if (bonus)
         return scan_rows<2>(is_bf16, q, q_stride, k, k_stride, v, v_stride, decay, cu_q, slots, n_seqs, state, slot_stride, s_offset,
-                            n_heads, n_groups, dim, vdim, q_scale, y, bonus, stream);
+                            n_heads, n_groups, dim, vdim, q_scale, y, bonus, decay_bias, decay_kind, inv_tau, stream);
     return scan_rows<1>(is_bf16, q, q_stride, k, k_stride, v, v_stride, decay, cu_q, slots, n_seqs, state, slot_stride, s_offset,
-                        n_heads, n_groups, dim, vdim, q_scale, y, bonus, stream);
+                        n_heads, n_groups, dim, vdim, q_scale, y, bonus, decay_bias, decay_kind, inv_tau, stream);
 }
 
 // ------------------------------------------------------------------------------------------------------------------

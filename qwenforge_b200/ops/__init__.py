@@ -7,12 +7,12 @@ from .kernels import (TC_PLAIN, TC_SWIGLU, tc_gemm, tc_gemm_takes, tc_gemm_is_pe
                       gated_group_norm, causal_conv_silu, OUTER_STATE_MAX_DIM, CONV_MAX_TAPS, ACTIVATIONS,
                       add_dyt_norm, add_dyt_norm_shift, residual_add_pair, stream_pair, head_gate, pool_cache_write, causal_conv,
                       add_rms_norm_scaled, residual_add_scaled, rms_norm_cols, mix_rows, bias_glu, shift_mix, channel_decay,
-                      outer_state_scan_rows)
+                      outer_state_scan_rows, rows_prepare)
 from .linear import linear, linear_rows, gated_rows, own_tensor_core_products, use_own_tensor_core_products
 
 __all__ = [
     "add_rms_norm_scaled", "residual_add_scaled", "rms_norm_cols", "mix_rows", "bias_glu", "shift_mix", "channel_decay",
-    "outer_state_scan_rows",
+    "outer_state_scan_rows", "rows_prepare",
     "add_dyt_norm", "add_dyt_norm_shift", "residual_add_pair", "stream_pair", "head_gate", "pool_cache_write", "causal_conv",
     "bias_act", "softcap_", "stabilized_gates", "decay_gates", "outer_state_scan", "gated_group_norm", "causal_conv_silu",
     "OUTER_STATE_MAX_DIM", "CONV_MAX_TAPS", "ACTIVATIONS",

@@ -1242,17 +1242,21 @@ def latent_norm_cache(down: torch.Tensor, q_rank: int, q_norm: Optional[torch.Te
         _I(1 if write_cache else 0), _I(n), _ptr(err), _stream()), "latent_norm_cache")
 
 
-def _grouped(x, weight, out, a_group_cols, c_group_cols, rows, plan, a_rows=None, gated=False, row_scale=None, clamp=None) -> None:
+def _grouped(x, weight, out, a_group_cols, c_group_cols, rows, plan, a_rows=None, gated=False, row_scale=None, clamp=None,
+             activation=None) -> None:
     groups, n, k = weight.shape
     if gated:
         n //= 2   # columns of the result
     limit, alpha = (float(clamp[0]), float(clamp[1])) if clamp is not None else (0.0, 0.0)
-    code = library("grouped_gemm").qf_grouped_gemm_gate(
+    if activation is not None and (gated or activation not in ACTIVATIONS):
+        raise KernelError(f"grouped_gemm: activation {activation!r} is not known, or was asked of a gated product")
+    code = library("grouped_gemm").qf_grouped_gemm_act(
         _I(_is_bf16(x.dtype)), _ptr(x), _LL(x.stride(0)), _LL(a_group_cols), _ptr(weight), _LL(weight.stride(0)),
         _LL(weight.stride(1)), _ptr(out), _LL(out.stride(0)), _LL(c_group_cols), _I(rows), _I(n), _I(k), _I(groups),
         _ptr(plan.tile_group if plan else None), _ptr(plan.tile_row0 if plan else None), _ptr(plan.offsets if plan else None),
         _ptr(plan.n_tiles if plan else None), _I(plan.max_tiles if plan else 0), _I(plan.tile_rows if plan else 0),
-        _ptr(a_rows), _I(int(gated)), _ptr(row_scale), _F(limit), _F(alpha), _stream())
+        _ptr(a_rows), _I(int(gated)), _ptr(row_scale), _F(limit), _F(alpha), _I(0 if activation is None else ACTIVATIONS[activation] + 1),
+        _stream())
     if code == 1:
         raise KernelError("grouped_gemm: the plan's tiles do not fit these operands (tiles of 128 rows need bfloat16 operands "
                           "whose K and strides are multiples of 8), or the grid is too large")
@@ -1414,17 +1418,19 @@ def moe_combine(y: torch.Tensor, plan: MoePlan, out: torch.Tensor, scale_output:
                                                 _ptr(gate_weight if gate_k else None), _I(gate_k), _stream()), "moe_combine")
 
 
-def expert_linear(x: torch.Tensor, weight: torch.Tensor, plan: MoePlan, out: torch.Tensor, gather: bool = False) -> None:
+def expert_linear(x: torch.Tensor, weight: torch.Tensor, plan: MoePlan, out: torch.Tensor, gather: bool = False,
+                  activation: Optional[str] = None) -> None:
     """out[row] = x[row] @ weight[expert of the row].T for rows sorted by expert (`plan`): x [T * top, K], weight [E, N, K],
     out [T * top, N], all of the activation dtype; one launch, no count on the host. With `gather`, x is the tokens' own
-    rows [T, K] and row r reads x[token of r]: the sorted rows are never stored."""
+    rows [T, K] and row r reads x[token of r]: the sorted rows are never stored. With `activation` (a name of `ACTIVATIONS`)
+    the product's epilogue applies it to the float32 sums before they are stored."""
     _dev("x", x)
     _dev("weight", weight, x.dtype)
     _dev("out", out, x.dtype)
     groups, n, k = weight.shape
     if groups != plan.n_experts or x.shape != ((plan.n_tokens if gather else plan.pairs), k) or out.shape != (plan.pairs, n):
         raise KernelError(f"expert_linear: shapes {tuple(x.shape)} x {tuple(weight.shape)} -> {tuple(out.shape)} do not agree")
-    _grouped(x, weight, out, 0, 0, plan.pairs, plan, plan.sorted_token if gather else None)
+    _grouped(x, weight, out, 0, 0, plan.pairs, plan, plan.sorted_token if gather else None, activation=activation)
 
 
 def expert_gate_takes(x: torch.Tensor, weight: torch.Tensor, plan: MoePlan) -> bool:
@@ -1855,12 +1861,14 @@ def channel_decay(pre: torch.Tensor, bias: Optional[torch.Tensor], kind: str, ou
 
 def outer_state_scan_rows(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, cu_q: torch.Tensor,
                           slots: torch.Tensor, state: torch.Tensor, s_offset: int, n_heads: int, dim: int, vdim: int,
-                          q_scale: float, y: torch.Tensor, bonus: Optional[torch.Tensor] = None) -> None:
+                          q_scale: float, y: torch.Tensor, bonus: Optional[torch.Tensor] = None, decay_from=None) -> None:
     """The recurrence of a matrix state per head with a decay per row of the state, float32 inside:
         S <- diag(decay_t) S + k_t v_t^T,   y_t = S^T (q_scale q_t)                         (bonus None: read after the update)
         y_t = (S + diag(bonus) k_t v_t^T)^T (q_scale q_t),  then the same update            (bonus float32 [heads, dim])
     q, k: [T, heads * dim], v: [T, heads * vdim] in the activation dtype (rows may be strided); decay float32 [T, heads * dim];
-    y float32 [T, heads * vdim]; S in `state` at s_offset as [heads, dim, vdim]."""
+    y float32 [T, heads * vdim]; S in `state` at s_offset as [heads, dim, vdim].
+    `decay_from` = (kind, bias float32 [heads * dim], tau): `decay` holds the decays' pre-activations instead, and the kernel forms
+    the decays on its way in, with the arithmetic of `channel_decay` (kind "double_exp" or "sigmoid_root")."""
     for name, t in (("q", q), ("k", k), ("v", v)):
         _rows(name, t, q.dtype)
     _is_bf16(q.dtype)
@@ -1877,8 +1885,53 @@ def outer_state_scan_rows(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, dec
         _dev("bonus", bonus, torch.float32)
         if bonus.numel() != n_heads * dim:
             raise KernelError("outer_state_scan_rows: bonus must be float32 [heads, dim]")
+    kind, decay_bias, inv_tau = 0, None, 1.0
+    if decay_from is not None:
+        name, decay_bias, tau = decay_from
+        if name not in DECAYS or tau <= 0:
+            raise KernelError("outer_state_scan_rows: decay_from names 'double_exp' or 'sigmoid_root' and a positive tau")
+        _dev("decay bias", decay_bias, torch.float32)
+        if decay_bias.numel() != n_heads * dim:
+            raise KernelError("outer_state_scan_rows: the decays' bias must be float32 [heads * dim]")
+        kind, inv_tau = DECAYS[name] + 1, 1.0 / tau
     _state(state, (s_offset, n_heads * dim * vdim))
     _check(library("recurrent").qf_outer_state_scan_rows(
         _I(_is_bf16(q.dtype)), _ptr(q), _I(q.stride(0)), _ptr(k), _I(k.stride(0)), _ptr(v), _I(v.stride(0)), _ptr(decay), _ptr(cu_q),
         _ptr(slots), _I(cu_q.numel() - 1), _ptr(state), _LL(state.stride(0)), _LL(s_offset), _I(n_heads), _I(n_heads), _I(dim),
-        _I(vdim), _F(q_scale), _ptr(y), _ptr(bonus), _stream()), "outer_state_scan_rows")
+        _I(vdim), _F(q_scale), _ptr(y), _ptr(bonus), _ptr(decay_bias), _I(kind), _F(inv_tau), _stream()), "outer_state_scan_rows")
+
+
+def rows_prepare(x: torch.Tensor, runs, eps: float, mix=None) -> None:
+    """What stands between a q | k | v product and the rotation where q and k are normed over whole rows, in place and in one
+    launch. `runs`: up to three of (first column, width, count, bias or None, weight or None): the run gets its bias, then (with
+    count > 0) the RMS norm x / sqrt(sum(x^2) / count + eps) * weight. `mix` = (run index, other [T, ...], heads' size, head pitch
+    in x, head pitch in other, weight): that run, after its bias, is drawn towards `other` head by head,
+    (1 - weight) * x + weight * other. Float32 inside; x [T, C] with unit inner stride."""
+    _rows("x", x)
+    _is_bf16(x.dtype)
+    runs = list(runs)
+    if not 1 <= len(runs) <= 3:
+        raise KernelError("rows_prepare: one to three runs of columns")
+    n = len(runs)
+    col0, width, count = ((_I * n)(*[int(r[i]) for r in runs]) for i in range(3))
+    for c0, w, cnt, bias, weight in runs:
+        if c0 < 0 or w <= 0 or c0 + w > x.shape[1] or not 0 <= cnt <= w or (cnt > 0 and weight is None):
+            raise KernelError("rows_prepare: a run must lie within the row; a norm needs its weight")
+        for name, t in (("bias", bias), ("weight", weight)):
+            if t is not None:
+                _dev(name, t, x.dtype)
+                if t.numel() != w:
+                    raise KernelError(f"rows_prepare: {name} must hold one element per column of its run")
+    biases = (_P * n)(*[(0 if r[3] is None else r[3].data_ptr()) for r in runs])
+    weights = (_P * n)(*[(0 if r[4] is None else r[4].data_ptr()) for r in runs])
+    mix_run, other, ldo, size, x_head, other_head, lam = -1, None, 0, 0, 1, 1, 0.0
+    if mix is not None:
+        mix_run, other, size, x_head, other_head, lam = mix
+        _rows("other", other, x.dtype)
+        heads = -(-runs[mix_run][1] // x_head)
+        if other.shape[0] != x.shape[0] or size > min(x_head, other_head) or (heads - 1) * other_head + size > other.shape[1]:
+            raise KernelError("rows_prepare: the heads of the mixed run do not fit the other rows")
+        ldo = other.stride(0)
+    _check(library("norm").qf_rows_prepare(_I(_is_bf16(x.dtype)), _ptr(x), _I(x.stride(0)), _I(x.shape[0]), _I(n), col0, width, count,
+                                           biases, weights, _I(mix_run), _ptr(other), _I(ldo), _I(size), _I(x_head), _I(other_head),
+                                           _F(lam), _F(eps), _stream()), "rows_prepare")

@@ -21,7 +21,7 @@ TIMED = ("embed_gather", "gather_rows", "add_rms_norm", "residual_add", "linear"
          "moe_combine", "tc_gemm_grouped", "scaled_swiglu", "linear_rows", "bias_act", "softcap_", "outer_state_scan", "stabilized_gates",
          "decay_gates", "gated_group_norm", "causal_conv_silu", "causal_conv", "add_dyt_norm", "add_dyt_norm_shift", "residual_add_pair", "stream_pair",
          "head_gate", "pool_cache_write", "add_rms_norm_scaled", "residual_add_scaled", "rms_norm_cols", "mix_rows", "bias_glu",
-         "shift_mix", "channel_decay", "outer_state_scan_rows")
+         "shift_mix", "channel_decay", "outer_state_scan_rows", "rows_prepare")
 
 
 class KernelTimer:

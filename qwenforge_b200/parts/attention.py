@@ -283,13 +283,10 @@ class GqaAttention(Mixer):
         late_bias = self.qkv_bias_t
         if self.row_norm_eps is not None or self.value_mix is not None:
             # what follows reads q, k and v with their biases: the bias joins the product, not the rotation kernel
-            qkv = ops.linear(x, self.qkv_weight, self.qkv_bias_t) if self.qkv_bias_t is not None else ops.linear_rows(x, self.qkv_weight)
+            # (biases, both norms and the values' mixing are one kernel behind the product)
+            qkv = ops.linear_rows(x, self.qkv_weight)
             late_bias = None
-            if self.row_norm_eps is not None:
-                ops.rms_norm_cols(qkv, ((0, self.q_width, self.n_heads * self.key_dim, self.q_row_norm),
-                                        (self.q_width, self.kv_width, self.n_kv * self.key_dim, self.k_row_norm)), self.row_norm_eps)
-            if self.value_mix is not None:
-                self._mix_values(qkv, ctx)
+            self._prepare_rows(qkv, ctx)
         else:
             qkv = ops.linear_rows(x, self.qkv_weight)           # [T, q | k | v (| gates)]
         gates = qkv[:, self.qkv_width:self.qkv_width + self.n_heads] if self.gated else None
@@ -330,21 +327,30 @@ class GqaAttention(Mixer):
             ops.head_gate(attended, gates, self.n_heads)
         return ops.linear(attended, self.o_weight, self.o_bias_t) if self.o_bias_t is not None else ops.linear_rows(attended, self.o_weight)
 
-    def _mix_values(self, qkv, ctx) -> None:
-        """The chain of layers that share values through one step: the source leaves its values (a view of its projection's
-        output, kept alive by the step's memo) for the layers after it; a mixing layer draws its own towards them in place."""
-        key = ("gqa_attention.value_mix", self.value_mix["key"])
-        memo = ctx.step_memo if ctx.step_memo is not None else {}
-        values = qkv[:, self.q_width + self.kv_width:self.q_width + 2 * self.kv_width]
-        if self.value_mix["role"] == "source":
-            memo[key] = (values, self.n_kv, self.value_dim, self.head_dim)
-            return
-        if key not in memo:
-            raise RuntimeError("gqa_attention: a layer mixes in the values of a layer that has not run in this step")
-        source, heads, size, source_head = memo[key]
-        if (heads, size) != (self.n_kv, self.value_dim):
-            raise ValueError("gqa_attention: layers that mix their values have as many key/value heads of the same value size")
-        ops.mix_rows(values, source, self.n_kv, self.value_dim, self.head_dim, source_head, self.mix_weight)
+    def _prepare_rows(self, qkv, ctx) -> None:
+        """Biases, the norms of q and k over their whole rows and the chain of layers that share values, in one launch on the
+        product's output: the chain's source leaves its values (a view of this output, kept alive by the step's memo) for
+        the layers after it; a mixing layer draws its own towards them in place."""
+        q_w, kv_w, b = self.q_width, self.kv_width, self.qkv_bias_t
+        piece = lambda lo, hi: None if b is None else b[lo:hi]
+        normed = self.row_norm_eps is not None
+        runs = [(0, q_w, self.n_heads * self.key_dim if normed else 0, piece(0, q_w), self.q_row_norm),
+                (q_w, kv_w, self.n_kv * self.key_dim if normed else 0, piece(q_w, q_w + kv_w), self.k_row_norm),
+                (q_w + kv_w, kv_w, 0, piece(q_w + kv_w, q_w + 2 * kv_w), None)]
+        mix = None
+        if self.value_mix is not None:
+            key = ("gqa_attention.value_mix", self.value_mix["key"])
+            memo = ctx.step_memo if ctx.step_memo is not None else {}
+            if self.value_mix["role"] == "source":
+                memo[key] = (qkv[:, q_w + kv_w:q_w + 2 * kv_w], self.n_kv, self.value_dim, self.head_dim)
+            else:
+                if key not in memo:
+                    raise RuntimeError("gqa_attention: a layer mixes in the values of a layer that has not run in this step")
+                source, heads, size, source_head = memo[key]
+                if (heads, size) != (self.n_kv, self.value_dim):
+                    raise ValueError("gqa_attention: layers that mix their values have as many key/value heads of the same value size")
+                mix = (2, source, self.value_dim, self.head_dim, source_head, self.mix_weight)
+        ops.rows_prepare(qkv, runs, self.row_norm_eps if normed else 0.0, mix)
 
     # ---- the form for decode steps of up to 64 sequences that works on the residual stream in place: the norm, bias,
     # rotation and cache write ride on the QKV product and the addition on the output projection wherever a kernel of

@@ -170,9 +170,8 @@ class RoutedExperts(FeedForward):
                 y = torch.empty_like(rows)
                 ops.tc_gemm_grouped(ops.TC_PLAIN, act, self.down, plan, y, None, ctx.err)
                 return RowSum(y, plan.dest, self.top, plan.sorted_weight)
-            up = torch.empty_like(act)
-            ops.expert_linear(x, self.gate_up, plan, up, gather=True)   # the rows are read through the plan's row map
-            ops.bias_act(up, None, self.activation, act)
+            # the rows are read through the plan's row map; the activation in the first product's epilogue
+            ops.expert_linear(x, self.gate_up, plan, act, gather=True, activation=self.activation)
             ops.expert_linear(act, self.down, plan, rows)
             return RowSum(rows, plan.dest, self.top, plan.sorted_weight)
         if self.gate == "clamped":

@@ -173,9 +173,22 @@ class StateSpace(Mixer):
         return ops.linear_rows(out, self.o_weight)
 
 
-def _low_rank(params, key="rank") -> int:
+def _rank_of(params, key="rank") -> int:
     """The rank of a low-rank pair of matrices: named by the spec, or -1 where only the weight files give it."""
     return int(params[key]) if params.get(key) else -1
+
+
+def _low_rank(x, first, second, activation):
+    """second act(first x) with float32 sums out: two products and the activation between them; the middle carries the
+    activation dtype. (One kernel for both products of a step of few rows was measured at 29 and 48 microseconds against 13
+    for the three launches at widths 896 and 2,048: the weight streamer has all of a product's weight bytes on their way at
+    once, and a kernel that walks the rank row by row pays a round trip to memory per group of rows.)"""
+    low = ops.linear_rows(x, first)
+    if activation is not None:
+        bent = torch.empty_like(low)
+        ops.bias_act(low, None, activation, bent)
+        low = bent
+    return ops.linear_rows(low, second, out_dtype=torch.float32)
 
 
 class TimeMix(Mixer):
@@ -190,7 +203,7 @@ class TimeMix(Mixer):
         super().__init__(spec)
         p = self.params
         self.hidden, self.n_heads, self.dim = int(p["hidden_size"]), int(p["num_heads"]), int(p["head_dim"])
-        self.eps, self.rank = float(p["eps"]), _low_rank(p)
+        self.eps, self.rank = float(p["eps"]), _rank_of(p)
         if self.dim > ops.OUTER_STATE_MAX_DIM:
             raise ValueError(f"time_mix: head_dim {self.dim} > {ops.OUTER_STATE_MAX_DIM} is not supported by the scan kernel")
         self.inner = self.n_heads * self.dim
@@ -239,15 +252,10 @@ class TimeMix(Mixer):
                 ops.linear(mixes[:, i * w:(i + 1) * w], self.proj_weight[i], out=proj[:, i * c:(i + 1) * c])
         else:                       # one launch for the four
             ops.head_linear(mixes[:, :4 * w], self.proj_weight, proj)
-        low = ops.linear_rows(mixes[:, 4 * w:], self.w1)
-        bent = torch.empty_like(low)
-        ops.bias_act(low, None, "tanh", bent)
-        pre = ops.linear_rows(bent, self.w2, out_dtype=torch.float32)                    # float32 sums
-        decay = torch.empty((n, c), **f32)
-        ops.channel_decay(pre, self.w0, "double_exp", decay)
-        y = torch.empty((n, c), **f32)
-        ops.outer_state_scan_rows(proj[:, :c], proj[:, c:2 * c], proj[:, 2 * c:3 * c], decay, ctx.cu_q, ctx.slots, site.storage,
-                                  self.s_offset, h, d, d, 1.0, y, bonus=self.bonus)
+        pre = _low_rank(mixes[:, 4 * w:], self.w1, self.w2, "tanh")                      # float32 sums
+        y = torch.empty((n, c), **f32)   # (the scan forms the decays exp(-exp(pre + w0)) on its way in)
+        ops.outer_state_scan_rows(proj[:, :c], proj[:, c:2 * c], proj[:, 2 * c:3 * c], pre, ctx.cu_q, ctx.slots, site.storage,
+                                  self.s_offset, h, d, d, 1.0, y, bonus=self.bonus, decay_from=("double_exp", self.w0, 1.0))
         out = torch.empty((n, c), dtype=x.dtype, device=x.device)
         ops.gated_group_norm(y, proj[:, 3 * c:], self.norm, self.eps, out, h, h, "silu", False)
         return ops.linear_rows(out, self.o_weight)
@@ -263,7 +271,7 @@ class GatedLinearAttention(Mixer):
         p = self.params
         self.hidden, self.n_heads = int(p["hidden_size"]), int(p["num_heads"])
         self.dim, self.vdim = int(p["head_dim"]), int(p["value_dim"])
-        self.tau, self.eps, self.rank = float(p["tau"]), float(p["eps"]), _low_rank(p)
+        self.tau, self.eps, self.rank = float(p["tau"]), float(p["eps"]), _rank_of(p)
         if self.dim > ops.OUTER_STATE_MAX_DIM or self.tau <= 0:
             raise ValueError(f"gated_linear_attention: head_dim up to {ops.OUTER_STATE_MAX_DIM} and a positive tau are supported")
         self.state_floats = self.n_heads * self.dim * self.vdim
@@ -300,12 +308,10 @@ class GatedLinearAttention(Mixer):
         n, h, d, v = x.shape[0], self.n_heads, self.dim, self.vdim
         f32 = dict(dtype=torch.float32, device=x.device)
         proj = ops.linear_rows(x, self.proj_weight)                                      # [T, q | k | v | g]
-        pre = ops.linear_rows(ops.linear_rows(x, self.a1), self.a2, out_dtype=torch.float32)   # float32 sums
-        decay = torch.empty((n, h * d), **f32)
-        ops.channel_decay(pre, self.a2_bias, "sigmoid_root", decay, tau=self.tau)
-        y = torch.empty((n, h * v), **f32)
-        ops.outer_state_scan_rows(proj[:, :h * d], proj[:, h * d:2 * h * d], proj[:, 2 * h * d:2 * h * d + h * v], decay, ctx.cu_q,
-                                  ctx.slots, site.storage, 0, h, d, v, d ** -0.5, y)
+        pre = _low_rank(x, self.a1, self.a2, None)                                       # float32 sums
+        y = torch.empty((n, h * v), **f32)   # (the scan forms the decays sigmoid(pre + b)^(1 / tau) on its way in)
+        ops.outer_state_scan_rows(proj[:, :h * d], proj[:, h * d:2 * h * d], proj[:, 2 * h * d:2 * h * d + h * v], pre, ctx.cu_q,
+                                  ctx.slots, site.storage, 0, h, d, v, d ** -0.5, y, decay_from=("sigmoid_root", self.a2_bias, self.tau))
         out = torch.empty((n, h * v), dtype=x.dtype, device=x.device)
         ops.gated_group_norm(y, proj[:, 2 * h * d + h * v:], self.norm, self.eps, out, h, h, "silu", False)
         return ops.linear_rows(out, self.o_weight)

@@ -326,9 +326,10 @@ def moe_combine(y, plan, out, scale_output, extra=None, extra_gate=None, gate_in
     out.copy_(total.to(out.dtype))
 
 
-def expert_linear(x, weight, plan, out, gather=False):
+def expert_linear(x, weight, plan, out, gather=False, activation=None):
     rows = _f(x)[plan.sorted_token.long()] if gather else _f(x)
-    out.copy_(torch.einsum("rk,rnk->rn", rows, _f(weight)[plan.row_expert]).to(out.dtype))
+    y = torch.einsum("rk,rnk->rn", rows, _f(weight)[plan.row_expert])
+    out.copy_((y if activation is None else _act(y, activation)).to(out.dtype))
 
 
 def bias_act(x, bias, kind, out):
@@ -384,6 +385,18 @@ def mix_rows(x, other, heads, size, x_head, other_head, weight):
         mine.copy_(((1.0 - weight) * _f(mine) + weight * _f(theirs)).to(x.dtype))
 
 
+def rows_prepare(x, runs, eps, mix=None):
+    for index, (col0, width, count, bias, weight) in enumerate(runs):
+        view = x[:, col0:col0 + width]
+        if bias is not None:
+            view.copy_((_f(view) + _f(bias)).to(x.dtype))
+        if mix is not None and mix[0] == index:
+            _, other, size, x_head, other_head, lam = mix
+            mix_rows(view, other, -(-width // x_head), size, x_head, other_head, lam)
+        if count > 0:
+            rms_norm_cols(x, ((col0, width, count, weight),), eps)
+
+
 def shift_mix(h, mu, cu_q, tok_seq, slots, state, offset, out, single=False):
     width = h.shape[1]
     for s in range(cu_q.numel() - 1):
@@ -405,8 +418,12 @@ def channel_decay(pre, bias, kind, out, tau=1.0):
     out.copy_(w.float())
 
 
-def outer_state_scan_rows(q, k, v, decay, cu_q, slots, state, s_offset, n_heads, dim, vdim, q_scale, y, bonus=None):
+def outer_state_scan_rows(q, k, v, decay, cu_q, slots, state, s_offset, n_heads, dim, vdim, q_scale, y, bonus=None, decay_from=None):
     size = n_heads * dim * vdim
+    if decay_from is not None:
+        made = torch.empty_like(decay)
+        channel_decay(decay, decay_from[1], decay_from[0], made, tau=decay_from[2])
+        decay = made
     for s in range(cu_q.numel() - 1):
         slot = int(slots[s])
         S = torch.zeros(n_heads, dim, vdim, dtype=torch.float64, device=q.device)
@@ -565,7 +582,7 @@ def pool_cache_write(cu_q, tok_pos, slots, site, blocks, pool, max_q_len, err):
             blocks.storage[page, 1, :, block % PAGE, :] = v.mean(1).to(blocks.storage.dtype)
 
 
-ALL = dict(bias_glu=bias_glu, add_rms_norm_scaled=add_rms_norm_scaled, residual_add_scaled=residual_add_scaled, rms_norm_cols=rms_norm_cols,
+ALL = dict(rows_prepare=rows_prepare, bias_glu=bias_glu, add_rms_norm_scaled=add_rms_norm_scaled, residual_add_scaled=residual_add_scaled, rms_norm_cols=rms_norm_cols,
            mix_rows=mix_rows, shift_mix=shift_mix, channel_decay=channel_decay, outer_state_scan_rows=outer_state_scan_rows,
            gated_rows=gated_rows, causal_conv=causal_conv, add_dyt_norm=add_dyt_norm, add_dyt_norm_shift=add_dyt_norm_shift, residual_add_pair=residual_add_pair, stream_pair=stream_pair,
            head_gate=head_gate, pool_cache_write=pool_cache_write, bias_act=bias_act, softcap_=softcap_, stabilized_gates=stabilized_gates, decay_gates=decay_gates,

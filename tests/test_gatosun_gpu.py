@@ -120,6 +120,49 @@ def test_norms_over_runs_of_columns_and_rows_drawn_towards_other_rows(dtype):
 
 
 @pytest.mark.parametrize("dtype", BOTH)
+def test_biases_row_norms_and_value_mixing_in_one_launch(dtype):
+    """The one kernel behind a q | k | v product against the steps it stands for; heads of q and k padded beyond their size."""
+    from qwenforge_b200 import ops
+    g = torch.Generator().manual_seed(4)
+    n, q_w, kv_w = 21, 48, 24                      # 4 heads of 12 (10 used), 2 kv heads of 12 (values: 7 used)
+    x = rand(g, n, q_w + 2 * kv_w + 5, dtype=dtype, spread=2.0)
+    pad = torch.zeros(q_w + 2 * kv_w, dtype=torch.bool)
+    for h in range(6):
+        pad[h * 12 + 10:h * 12 + 12] = True
+    for h in range(2):
+        pad[q_w + kv_w + h * 12 + 7:q_w + kv_w + (h + 1) * 12] = True
+    x[:, :q_w + 2 * kv_w][:, pad.to(DEV)] = 0
+    bias = rand(g, q_w + 2 * kv_w, dtype=dtype)
+    bias[pad.to(DEV)] = 0
+    wq, wk, other = rand(g, q_w, dtype=dtype), rand(g, kv_w, dtype=dtype), rand(g, n, 30, dtype=dtype)
+    for with_bias in (True, False):
+        for mix in (None, (2, other[:, 3:], 7, 12, 9, 0.35)):
+            b = (lambda lo, hi: bias[lo:hi]) if with_bias else (lambda lo, hi: None)
+            cpu = lambda t: None if t is None else t.cpu()
+            runs = [(0, q_w, 40, b(0, q_w), wq), (q_w, kv_w, 20, b(q_w, q_w + kv_w), wk), (q_w + kv_w, kv_w, 0, b(q_w + kv_w, q_w + 2 * kv_w), None)]
+            got, want = x.clone(), x.clone().cpu()
+            ops.rows_prepare(got, runs, 1e-5, mix)
+            refs.rows_prepare(want, [(c, w, k, cpu(bb), cpu(ww)) for c, w, k, bb, ww in runs], 1e-5,
+                              None if mix is None else (mix[0], mix[1].cpu(), *mix[2:]))
+            close(got, want, dtype, f"bias {with_bias} mix {mix is not None}", bf16=1.6e-2)
+            assert torch.equal(got[:, q_w + 2 * kv_w:], x[:, q_w + 2 * kv_w:])
+
+
+@pytest.mark.parametrize("dtype", BOTH)
+@pytest.mark.parametrize("k,n", [(44, 14), (128, 64)])
+def test_activation_in_the_experts_first_product(dtype, k, n):
+    from qwenforge_b200 import ops
+    g = torch.Generator().manual_seed(k)
+    x, router, weight = rand(g, 50, k, dtype=dtype), rand(g, 6, k, dtype=dtype), rand(g, 6, n, k, dtype=dtype, spread=k ** -0.5)
+    plan = ops.moe_plan(None, 2, x=x, router=router)
+    plain_out, out = torch.empty(100, n, dtype=dtype, device=DEV), torch.empty(100, n, dtype=dtype, device=DEV)
+    ops.expert_linear(x, weight, plan, plain_out, gather=True)
+    ops.expert_linear(x, weight, plan, out, gather=True, activation="relu2")
+    want = torch.relu(plain_out.float()) ** 2
+    close(out, want, dtype, "relu2 behind the product", f32=1e-6, bf16=1e-2)
+
+
+@pytest.mark.parametrize("dtype", BOTH)
 @pytest.mark.parametrize("inter", [30, 256])
 def test_gated_activation_with_biases(dtype, inter):
     from qwenforge_b200 import ops
