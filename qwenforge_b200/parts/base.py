@@ -95,6 +95,47 @@ class Part:
         return []
 
 
+# ---- two chains of kernels side by side. A step of few rows is a chain of short dependent kernels; where a part has two
+# chains that do not depend on each other (two mixers on one input, a shared expert beside the routed ones) the second runs on
+# a stream of its own: `fork` makes it wait for the step's stream, `join` makes the step's stream wait for it. A capture of
+# the step's stream takes both with it. Long steps fill the GPU with either chain and gain nothing.
+SIDE_BY_SIDE_MAX_ROWS = 64
+_side_streams: dict = {}
+
+
+def runs_side_by_side(x: torch.Tensor) -> bool:
+    """Whether a part with two independent chains should put the second on the side stream for this step's input."""
+    return x.is_cuda and x.shape[0] <= SIDE_BY_SIDE_MAX_ROWS
+
+
+def fork(x: torch.Tensor):
+    """(the current stream, a side stream), the side stream waiting for what the current stream has issued so far. `x`, which
+    the side stream will read, is marked as in use there. A part that already runs on a side stream gets the next one of the
+    device's pool, so chains may fork inside chains."""
+    index = x.device.index if x.device.index is not None else torch.cuda.current_device()
+    pool = _side_streams.setdefault(index, [])
+    main = torch.cuda.current_stream(x.device)
+    depth = next((i + 1 for i, s in enumerate(pool) if s == main), 0)
+    while len(pool) <= depth:
+        pool.append(torch.cuda.Stream(device=index))
+    side = pool[depth]
+    event = torch.cuda.Event()
+    event.record(main)
+    side.wait_event(event)
+    x.record_stream(side)
+    return main, side
+
+
+def join(main, side, *made_on_side) -> None:
+    """The step's stream waits for the side stream; tensors made there and read from here on are marked as in use here."""
+    event = torch.cuda.Event()
+    event.record(side)
+    main.wait_event(event)
+    for t in made_on_side:
+        if t is not None:
+            t.record_stream(main)
+
+
 class Pending:
     """What a block may leave in the place of a plain pending output: something that still has to reach the residual
     stream and knows how (`add_to`). A block that can fold it into its own first kernel names its class in

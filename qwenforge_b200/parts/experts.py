@@ -31,7 +31,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from .base import FeedForward, RowSum, TensorSpec
+from .base import FeedForward, RowSum, TensorSpec, fork, join, runs_side_by_side
 from .registry import register_part
 
 
@@ -122,21 +122,33 @@ class RoutedExperts(FeedForward):
         return [w for w in (self.router, self.gate_up, self.down, self.bias, self.correction, self.shared_gate_up, self.shared_down,
                             self.shared_logit) if w is not None]
 
+    def _shared_rows(self, x):
+        """The expert that every token gets: [T, W], not yet gated."""
+        act = torch.empty((x.shape[0], int(self.shared["size"])), dtype=x.dtype, device=x.device)
+        if self.gate == "none":
+            ops.bias_act(ops.linear_rows(x, self.shared_gate_up), None, self.activation, act)
+        elif self.gate == "clamped":
+            limit = float(self.shared.get("limit") or self.limit)
+            if not ops.gated_rows(x, self.shared_gate_up, act, clamp=(limit, self.alpha)):   # few rows: the gate in the product
+                ops.clamped_glu(ops.linear_rows(x, self.shared_gate_up), limit, self.alpha, act)
+        else:
+            ops.swiglu(ops.linear_rows(x, self.shared_gate_up), act)
+        return ops.linear_rows(act, self.shared_down)
+
     def forward(self, x, ctx):
         out = torch.empty_like(x)
-        r = self._routed_rows(x, ctx)
         extra = None
-        if self.shared is not None:   # the expert that every token gets rides on the kernel that sums the chosen ones
-            act = torch.empty((x.shape[0], int(self.shared["size"])), dtype=x.dtype, device=x.device)
-            if self.gate == "none":
-                ops.bias_act(ops.linear_rows(x, self.shared_gate_up), None, self.activation, act)
-            elif self.gate == "clamped":
-                limit = float(self.shared.get("limit") or self.limit)
-                if not ops.gated_rows(x, self.shared_gate_up, act, clamp=(limit, self.alpha)):   # few rows: the gate in the product
-                    ops.clamped_glu(ops.linear_rows(x, self.shared_gate_up), limit, self.alpha, act)
-            else:
-                ops.swiglu(ops.linear_rows(x, self.shared_gate_up), act)
-            extra = ops.linear_rows(act, self.shared_down)
+        if self.shared is not None and runs_side_by_side(x):
+            # a step of few rows: the shared expert's chain of kernels on a stream of its own beside the routed experts'
+            main, side = fork(x)
+            with torch.cuda.stream(side):
+                extra = self._shared_rows(x)
+            r = self._routed_rows(x, ctx)
+            join(main, side, extra)
+        else:
+            r = self._routed_rows(x, ctx)
+            if self.shared is not None:   # the expert that every token gets rides on the kernel that sums the chosen ones
+                extra = self._shared_rows(x)
         # (the shared expert's gate, one logit per token, is formed inside the kernel that sums)
         ops.moe_combine(r.rows, self._plan, out, r.row_weight is not None, extra, None, x if self.shared_logit is not None else None,
                         self.shared_logit.view(-1) if self.shared_logit is not None else None)

@@ -38,7 +38,7 @@ import torch
 
 from .. import ops
 from ..cache import StateNeed
-from .base import Mixer, TensorSpec
+from .base import Mixer, TensorSpec, fork, join, runs_side_by_side
 from .registry import register_part
 
 
@@ -250,9 +250,16 @@ class TimeMix(Mixer):
         if n > ops.WIDE_MAX_ROWS:   # long steps: a library product per mix
             for i in range(4):
                 ops.linear(mixes[:, i * w:(i + 1) * w], self.proj_weight[i], out=proj[:, i * c:(i + 1) * c])
-        else:                       # one launch for the four
+            pre = _low_rank(mixes[:, 4 * w:], self.w1, self.w2, "tanh")                  # float32 sums
+        elif runs_side_by_side(mixes):   # few rows: the decays' chain of three kernels beside the four projections' one launch
+            main, side = fork(mixes)
+            with torch.cuda.stream(side):
+                pre = _low_rank(mixes[:, 4 * w:], self.w1, self.w2, "tanh")
             ops.head_linear(mixes[:, :4 * w], self.proj_weight, proj)
-        pre = _low_rank(mixes[:, 4 * w:], self.w1, self.w2, "tanh")                      # float32 sums
+            join(main, side, pre)
+        else:
+            ops.head_linear(mixes[:, :4 * w], self.proj_weight, proj)
+            pre = _low_rank(mixes[:, 4 * w:], self.w1, self.w2, "tanh")
         y = torch.empty((n, c), **f32)   # (the scan forms the decays exp(-exp(pre + w0)) on its way in)
         ops.outer_state_scan_rows(proj[:, :c], proj[:, c:2 * c], proj[:, 2 * c:3 * c], pre, ctx.cu_q, ctx.slots, site.storage,
                                   self.s_offset, h, d, d, 1.0, y, bonus=self.bonus, decay_from=("double_exp", self.w0, 1.0))
@@ -307,8 +314,15 @@ class GatedLinearAttention(Mixer):
             raise ValueError("gated_linear_attention: a recurrent state cannot be read from another schedule entry")
         n, h, d, v = x.shape[0], self.n_heads, self.dim, self.vdim
         f32 = dict(dtype=torch.float32, device=x.device)
-        proj = ops.linear_rows(x, self.proj_weight)                                      # [T, q | k | v | g]
-        pre = _low_rank(x, self.a1, self.a2, None)                                       # float32 sums
+        if runs_side_by_side(x):   # few rows: the decays' two products beside the projections' one
+            main, side = fork(x)
+            with torch.cuda.stream(side):
+                pre = _low_rank(x, self.a1, self.a2, None)
+            proj = ops.linear_rows(x, self.proj_weight)
+            join(main, side, pre)
+        else:
+            proj = ops.linear_rows(x, self.proj_weight)                                  # [T, q | k | v | g]
+            pre = _low_rank(x, self.a1, self.a2, None)                                   # float32 sums
         y = torch.empty((n, h * v), **f32)   # (the scan forms the decays sigmoid(pre + b)^(1 / tau) on its way in)
         ops.outer_state_scan_rows(proj[:, :h * d], proj[:, h * d:2 * h * d], proj[:, 2 * h * d:2 * h * d + h * v], pre, ctx.cu_q,
                                   ctx.slots, site.storage, 0, h, d, v, d ** -0.5, y, decay_from=("sigmoid_root", self.a2_bias, self.tau))

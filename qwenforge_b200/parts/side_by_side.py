@@ -6,7 +6,7 @@ next adds them in float32.
 
 In a step of few rows on a GPU the two sides run on two streams: the right side forks off the step's stream at the mixer's
 input and joins it again before the block goes on. Such a step is a chain of short dependent kernels, and two chains side by
-side are as long as the longer one (measured at Qwen2.5-0.5B sizes, batch 8: 2.29 -> 2.12 ms per decode step). A capture of
+side are as long as the longer one (measured at Qwen2.5-0.5B sizes, batch 8: 2.29 -> 2.12 ms per decode step; `fork` and `join` in `parts/base.py`). A capture of
 the step's stream takes the fork and the join with it. Long steps run one side after the other: there both sides' products
 fill the GPU, and a recurrent scan, which holds a few dozen SMs and is bound by its own chain of instructions, only slows
 down when another kernel's blocks share its SMs (a 2,048-token prompt: 8.88 ms on one stream, 9.0 on two, also with the left
@@ -16,20 +16,8 @@ from __future__ import annotations
 import torch
 
 from ..cache import BundleNeed
-from .base import Mixer, PendingScaled
+from .base import Mixer, PendingScaled, fork, join, runs_side_by_side
 from .registry import build_part, register_part
-
-
-_side_streams: dict = {}
-CONCURRENT_MAX_ROWS = 64   # rows of a step up to which the two sides run on two streams
-
-
-def _side_stream(device) -> "torch.cuda.Stream":
-    """One more stream per device, made at first use, for the side that forks off."""
-    index = device.index if device.index is not None else torch.cuda.current_device()
-    if index not in _side_streams:
-        _side_streams[index] = torch.cuda.Stream(device=index)
-    return _side_streams[index]
 
 
 class SideBySide(Mixer):
@@ -59,23 +47,15 @@ class SideBySide(Mixer):
         if not writes_cache:
             raise ValueError("side_by_side: two mixers with states of their own cannot read another entry's cache")
         pick = lambda name, side: site[name] if side.cache_need() is not None else None
-        if not (self.concurrent and x.is_cuda and x.shape[0] <= CONCURRENT_MAX_ROWS):
+        if not (self.concurrent and runs_side_by_side(x)):
             left = self.left.forward(x, ctx, pick("left", self.left), True)
             right = self.right.forward(x, ctx, pick("right", self.right), True)
             return PendingScaled(left, self.left_scale, right, self.right_scale)
-        main, side = torch.cuda.current_stream(x.device), _side_stream(x.device)
-        fork = torch.cuda.Event()
-        fork.record(main)
-        side.wait_event(fork)            # the right side starts where the mixer's input is ready
+        main, side = fork(x)             # the right side starts where the mixer's input is ready
         with torch.cuda.stream(side):
             right = self.right.forward(x, ctx, pick("right", self.right), True)
-            join = torch.cuda.Event()
-            join.record(side)
         left = self.left.forward(x, ctx, pick("left", self.left), True)
-        main.wait_event(join)            # whoever reads the pair next runs on the step's stream
-        # the right side's output was allocated on the side stream and is read on the step's stream; so is x the other way round
-        right.record_stream(main)
-        x.record_stream(side)
+        join(main, side, right)          # whoever reads the pair next runs on the step's stream
         return PendingScaled(left, self.left_scale, right, self.right_scale)
 
 
