@@ -59,11 +59,11 @@ GAT_ODD = config(53, 44, 1e-5, 0.6, [
 ])
 # sizes that the tensor-core kernels and 16-byte paths take
 GAT_FAST = config(320, 128, 1e-6, 0.8, [
-    layer(parallel(4, 1, 64, 64, 40, 32, 4, 32, rank=8), dense(256)),
-    layer(gla(2, 32, 64, tau=16.0, rank=8), moe(8, 2, 64, groups=(2, 1), shared=64)),
-    layer(attention(4, 2, 64, 32, 16, v_mix=True), moe(8, 4, 64, groups=(4, 2))),
+    layer(parallel(4, 2, 64, 64, 48, 16, 4, 32, rank=8), dense(256)),
+    layer(gla(4, 32, 64, tau=8.0, rank=8), moe(6, 2, 64, groups=(3, 1), shared=64)),
+    layer(attention(8, 2, 64, 32, 32, v_mix=True), moe(8, 4, 64, groups=(4, 2))),
     layer(parallel(2, 2, 32, 32, 70, 32, 2, 64, rank=16), moe(8, 2, 64, shared=128)),
-    layer(attention(4, 2, 32, 32, 32, v_mix=True), dense(128)),
+    layer(attention(8, 2, 32, 32, 16, v_mix=True), dense(128)),
 ])
 # values that a given model may happen to make equal or 1
 GAT_ONES = config(31, 32, 1e-5, 1.0, [

@@ -279,7 +279,7 @@ def tensor_shapes(cfg):
             shapes.update({q + "q": (a["heads"] * a["dim"], width), q + "k": (a["kv_heads"] * a["dim"], width),
                            q + "v": (a["kv_heads"] * a["vdim"], width), q + "o": (width, a["heads"] * a["vdim"])})
             q, inner = p + "mix.right.", b["heads"] * b["dim"]
-            rank = int(b.get("rank", 16))
+            rank = int(b["rank"])
             for s in "rkvgw":
                 shapes[q + "mu." + s] = (width,)
             for s in "rkvg":
@@ -287,7 +287,7 @@ def tensor_shapes(cfg):
             shapes.update({q + "w1": (rank, width), q + "w2": (inner, rank), q + "w0": (inner,), q + "u": (b["heads"], b["dim"]),
                            q + "norm": (inner,), q + "o": (width, inner)})
         else:
-            hd, hv, rank = m["heads"] * m["dim"], m["heads"] * m["vdim"], int(m.get("rank", 16))
+            hd, hv, rank = m["heads"] * m["dim"], m["heads"] * m["vdim"], int(m["rank"])
             q = p + "mix."
             shapes.update({q + "q": (hd, width), q + "k": (hd, width), q + "v": (hv, width), q + "g": (hv, width), q + "o": (width, hv),
                            q + "norm": (m["vdim"],), q + "a1": (rank, width), q + "a2": (hd, rank), q + "a2.b": (hd,)})
