@@ -6,8 +6,8 @@ next adds them in float32.
 
 In a step of few rows on a GPU the two sides run on two streams: the right side forks off the step's stream at the mixer's
 input and joins it again before the block goes on. Such a step is a chain of short dependent kernels, and two chains side by
-side are as long as the longer one (measured at Qwen2.5-0.5B sizes, batch 8: 2.29 -> 2.12 ms per decode step; `fork` and `join` in `parts/base.py`). A capture of
-the step's stream takes the fork and the join with it. Long steps run one side after the other: there both sides' products
+side are as long as the longer one (measured at Qwen2.5-0.5B sizes, batch 8: 2.29 -> 2.12 ms per decode step; `fork` and
+`join` in `parts/base.py`). A capture of the step's stream takes the fork and the join with it. Long steps run one side after the other: there both sides' products
 fill the GPU, and a recurrent scan, which holds a few dozen SMs and is bound by its own chain of instructions, only slows
 down when another kernel's blocks share its SMs (a 2,048-token prompt: 8.88 ms on one stream, 9.0 on two, also with the left
 side held back until the scan has started)."""
